@@ -5,7 +5,8 @@ values of `n_kv_heads` x `head_dim` per token, all of them, a window of the
 last `window`, or those of the current chunk of `chunk` positions), or with
 state bytes of fixed size.  Layers with
 equal requests share one group; every group has storage, a page pool and block
-tables of its own.
+tables of its own.  A request with `shared_kv` keeps ONE row per token that is read as key and as value
+(attention over a latent): the group has no value storage, and `v` names the keys' tensor.
 
 Storage of one group: K and V as [line][page][kv head][PAGE tokens][head_dim],
 one "line" per schedule entry that writes to the group.  A sequence's pages are
@@ -33,6 +34,7 @@ class KVRequest:
     window: int = 0  # 0: all keys; W > 0: the last W
     chunk: int = 0   # C > 0: only the keys of the query's own chunk [floor(p / C) C, p]
     v_head_dim: int = 0  # 0: as head_dim
+    shared_kv: bool = False  # one row per token serves as key and as value (a latent): there is no value storage
 
     @property
     def value_dim(self) -> int:
@@ -40,7 +42,8 @@ class KVRequest:
 
     @property
     def key(self):
-        return ("kv", self.n_kv_heads, self.head_dim, self.window, self.chunk, self.value_dim)
+        base = ("kv", self.n_kv_heads, self.head_dim, self.window, self.chunk, self.value_dim)
+        return base + ("shared",) if self.shared_kv else base
 
     def first_visible(self, position: int) -> int:
         """The first key position that a query at `position` can see."""
@@ -59,7 +62,7 @@ class KVRequest:
         first = requests[0]
         if all(r.window == first.window and r.chunk == first.chunk for r in requests):
             return first
-        return KVRequest(first.n_kv_heads, first.head_dim, 0, 0, first.v_head_dim)
+        return KVRequest(first.n_kv_heads, first.head_dim, 0, 0, first.v_head_dim, first.shared_kv)
 
 
 def pages_for(n_tokens: int) -> int:
@@ -90,7 +93,7 @@ class KVGroup:
 
     def bytes_per_token(self, itemsize: int) -> int:
         r = self.request
-        return self.n_lines * r.n_kv_heads * (r.head_dim + r.value_dim) * itemsize
+        return self.n_lines * r.n_kv_heads * (r.head_dim + (0 if r.shared_kv else r.value_dim)) * itemsize
 
     def attach_storage(self, k, v) -> None:
         self.k, self.v = k, v

@@ -31,6 +31,7 @@ GROUPS = {
     "recurrent": ["recurrent.cu"],
     "moe": ["moe.cu"],
     "moe_tc": ["moe_tc.cu"],
+    "latent": ["latent.cu"],
     "gemm_plain": ["gemm_plain.cu"],
     "head_prep": ["head_prep.cu"],
     "attention_plain": ["attention_plain.cu"],

@@ -4,7 +4,12 @@
 //   router:   z = W_r h + b in 32-bit; the `top` largest logits are chosen (the lower index wins a tie),
 //             their weights are the softmax over the chosen logits alone; `always` further rows per
 //             token name the experts E, E + 1, ... with weight 1 (experts that every token uses).
+//             score 1: the scores are sigmoid(z); the experts form `groups` equal groups of neighbours, a group's score
+//             is the sum of its two largest scores, only experts of the `keep` best groups can be chosen; the weights are
+//             the chosen scores divided by their sum (+ 1e-20), times `route_scale`.  With a gate row (row E of the
+//             router's matrix) the `always` rows are weighted by sigmoid(row E . h), which also goes to `gate_out`.
 //   gate|up:  a[r, j] = act(Wg[e_r] h_t)_j * (Wu[e_r] h_t)_j          r = t * rows_per_token + k
+//             (not gated: a[r, j] = act(Wu[e_r] h_t)_j)
 //   down:     y[k, t, :] = weight_r * Wd[e_r] a[r, :]                 32-bit, one slice per choice
 //
 // The slices y[k] are partial sums of the layer's update: whoever adds the update adds them in the
@@ -20,9 +25,11 @@
 
 #define MOE_ACT_SILU 1
 #define MOE_ACT_GELU_TANH 2
+#define MOE_ACT_RELU2 4
 
 __device__ __forceinline__ float moe_activate(int act, float z) {
     if (act == MOE_ACT_SILU) return z / (1.0f + expf(-z));
+    if (act == MOE_ACT_RELU2) { const float r = fmaxf(z, 0.f); return r * r; }
     return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
 }
 
@@ -88,10 +95,12 @@ template <typename TH, typename TW>
 __global__ void __launch_bounds__(1024)
 moe_router_kernel(const TH* __restrict__ h, size_t h_stride, const TW* __restrict__ w, VecRef bias, int E, int d, int top,
                   int always, const int* __restrict__ tok_seq, int* __restrict__ ids, float* __restrict__ wts,
-                  const float* __restrict__ logits) {
+                  const float* __restrict__ logits, int score, int groups, int keep, float route_scale, int gate_row,
+                  float* __restrict__ gate_out) {
     extern __shared__ float sm[];
     float* hrow = sm;       // d
-    float* z = sm + d;      // E
+    float* z = sm + d;      // E (+ 1 with a gate row)
+    const int rows = E + (gate_row ? 1 : 0);
     pdl_trigger();
     const int t = blockIdx.x, per = top + always;
     const bool real = tok_seq == nullptr || tok_seq[t] >= 0;
@@ -101,21 +110,62 @@ moe_router_kernel(const TH* __restrict__ h, size_t h_stride, const TW* __restric
             ids[(size_t)t * per + k] = -1;
             wts[(size_t)t * per + k] = 0.f;
         }
+        if (gate_out != nullptr && threadIdx.x == 0) gate_out[t] = 0.f;
         return;
     }
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
     if (logits != nullptr) {
-        for (int e = threadIdx.x; e < E; e += blockDim.x) z[e] = logits[(size_t)t * E + e] + (bias.p != nullptr ? bias.at(e) : 0.f);
+        for (int e = threadIdx.x; e < rows; e += blockDim.x)
+            z[e] = logits[(size_t)t * rows + e] + (bias.p != nullptr && e < E ? bias.at(e) : 0.f);
     } else {
         for (int i = threadIdx.x; i < d; i += blockDim.x) hrow[i] = to_f32(h[(size_t)t * h_stride + i]);
         __syncthreads();
-        for (int e = warp; e < E; e += n_warps) {
+        for (int e = warp; e < rows; e += n_warps) {
             const float s = warp_dot(w + (size_t)e * d, hrow, d, lane);
-            if (lane == 0) z[e] = s + (bias.p != nullptr ? bias.at(e) : 0.f);
+            if (lane == 0) z[e] = s + (bias.p != nullptr && e < E ? bias.at(e) : 0.f);
         }
     }
     __syncthreads();
     if (warp == 0) {
+        float always_w = 1.0f;
+        if (gate_row) {
+            always_w = 1.0f / (1.0f + expf(-z[E]));
+            if (gate_out != nullptr && lane == 0) gate_out[t] = always_w;
+        }
+        if (score == 1) {
+            for (int e = lane; e < E; e += 32) z[e] = 1.0f / (1.0f + expf(-z[e]));
+            __syncwarp();
+            if (groups > 1) {
+                // lane g: the sum of the two largest scores of group g; `keep` rounds of a warp-wide arg max
+                // (the lower group wins a tie) mark the groups whose experts stay
+                const int gsz = E / groups;
+                float gs = -CUDART_INF_F;
+                if (lane < groups) {
+                    float a = -CUDART_INF_F, b = -CUDART_INF_F;
+                    for (int e = lane * gsz; e < (lane + 1) * gsz; ++e) {
+                        const float v = z[e];
+                        if (v > a) { b = a; a = v; } else if (v > b) b = v;
+                    }
+                    gs = gsz > 1 ? a + b : a;
+                }
+                unsigned kept = 0u;
+                for (int k = 0; k < keep; ++k) {
+                    float best = gs;
+                    int best_g = lane < groups ? lane : 0x7fffffff;
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) {
+                        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+                        const int og = __shfl_xor_sync(0xffffffffu, best_g, o);
+                        if (ov > best || (ov == best && og < best_g)) { best = ov; best_g = og; }
+                    }
+                    if (best_g < groups) kept |= 1u << best_g;
+                    if (lane == best_g) gs = -CUDART_INF_F;
+                }
+                for (int e = lane; e < E; e += 32)
+                    if (!((kept >> (e / gsz)) & 1u)) z[e] = -CUDART_INF_F;
+                __syncwarp();
+            }
+        }
         // `top` rounds of a warp-wide arg max; the chosen logit is taken out by -inf
         float chosen = 0.f, first = 0.f, sum = 0.f;
         int chosen_id = -1;
@@ -133,7 +183,7 @@ moe_router_kernel(const TH* __restrict__ h, size_t h_stride, const TW* __restric
                 if (ov > best || (ov == best && oe < best_e)) { best = ov; best_e = oe; }
             }
             if (k == 0) first = best;
-            const float p = expf(best - first);
+            const float p = score == 1 ? best : expf(best - first);
             sum += p;
             if (lane == k) { chosen = p; chosen_id = best_e; }
             if (lane == 0 && best_e < E) z[best_e] = -CUDART_INF_F;
@@ -141,21 +191,25 @@ moe_router_kernel(const TH* __restrict__ h, size_t h_stride, const TW* __restric
         }
         if (lane < top) {
             ids[(size_t)t * per + lane] = chosen_id < E ? chosen_id : -1;
-            wts[(size_t)t * per + lane] = chosen / sum;
+            wts[(size_t)t * per + lane] = score == 1 ? chosen / (sum + 1e-20f) * route_scale : chosen / sum;
         }
         for (int k = lane; k < always; k += 32) {
             ids[(size_t)t * per + top + k] = E + k;
-            wts[(size_t)t * per + top + k] = 1.0f;
+            wts[(size_t)t * per + top + k] = always_w;
         }
     }
 }
 
 extern "C" int odin_moe_router(const void* h, int h_dtype, long long h_stride, const void* w, int w_dtype, const void* bias,
                                int bias_dtype, int T, int E, int d, int top, int always, const int* tok_seq, int* ids,
-                               float* wts, const float* logits, void* stream) {
+                               float* wts, const float* logits, int score, int groups, int keep, float route_scale,
+                               int gate_row, float* gate_out, void* stream) {
     if (T <= 0) return 0;
     if (E <= 0 || top <= 0 || top > 32 || top > E || always < 0 || d <= 0) return ODIN_ERR_UNSUPPORTED;
-    const size_t smem = (size_t)(d + E) * sizeof(float);
+    if (score != 0 && score != 1) return ODIN_ERR_BAD_ARG;
+    if (groups < 1 || groups > 32 || E % groups != 0 || keep < 1 || keep > groups || (long long)keep * (E / groups) < top)
+        return ODIN_ERR_UNSUPPORTED;
+    const size_t smem = (size_t)(d + E + 1) * sizeof(float);
     if (smem > 200 * 1024) return ODIN_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
     VecRef bv{bias, bias_dtype == ODIN_BF16};
@@ -168,7 +222,8 @@ extern "C" int odin_moe_router(const void* h, int h_dtype, long long h_stride, c
         if (smem > 48 * 1024)                                                                                        \
             cudaFuncSetAttribute(moe_router_kernel<TH, TW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
         odin_launch(moe_router_kernel<TH, TW>, dim3(T), dim3(threads), smem, s, (const TH*)h, (size_t)h_stride,      \
-                    (const TW*)w, bv, E, d, top, always, tok_seq, ids, wts, logits);                                 \
+                    (const TW*)w, bv, E, d, top, always, tok_seq, ids, wts, logits, score, groups, keep,             \
+                    route_scale, gate_row, gate_out);                                                                \
     } while (0)
     if (h_dtype == ODIN_BF16 && w_dtype == ODIN_BF16) GO(bf16, bf16);
     else if (h_dtype == ODIN_F32 && w_dtype == ODIN_F32) GO(float, float);
@@ -181,11 +236,11 @@ extern "C" int odin_moe_router(const void* h, int h_dtype, long long h_stride, c
 }
 
 // ------------------------------------------------------------ gate|up of the rows' own experts
-// grid (rows, column blocks).  w: [experts][2 ff][d], the ff gate rows before the ff up rows.
+// grid (rows, column blocks).  w: [experts][2 ff][d], the ff gate rows before the ff up rows (not gated: [experts][ff][d]).
 template <typename TH, typename TW>
 __global__ void __launch_bounds__(MOE_THREADS)
 moe_gate_up_kernel(const TH* __restrict__ h, size_t h_stride, const TW* __restrict__ w, const int* __restrict__ ids, int per,
-                   int ff, int d, int act, TH* __restrict__ out) {
+                   int ff, int d, int act, int gated, TH* __restrict__ out) {
     extern __shared__ float hrow[];  // d
     pdl_trigger();
     pdl_wait();
@@ -200,18 +255,18 @@ moe_gate_up_kernel(const TH* __restrict__ h, size_t h_stride, const TW* __restri
     }
     for (int i = threadIdx.x; i < d; i += blockDim.x) hrow[i] = to_f32(h[(size_t)t * h_stride + i]);
     __syncthreads();
-    const TW* we = w + (size_t)e * 2 * ff * d;
+    const TW* we = w + (size_t)e * (gated ? 2 : 1) * ff * d;
     for (int j = c0 + warp; j < min(ff, c0 + MOE_COLS); j += MOE_WARPS) {
         const float g = warp_dot(we + (size_t)j * d, hrow, d, lane);
-        const float u = warp_dot(we + (size_t)(ff + j) * d, hrow, d, lane);
-        if (lane == 0) orow[j] = from_f32<TH>(moe_activate(act, g) * u);
+        const float u = gated ? warp_dot(we + (size_t)(ff + j) * d, hrow, d, lane) : 1.0f;
+        if (lane == 0) orow[j] = from_f32<TH>(gated ? moe_activate(act, g) * u : moe_activate(act, g));
     }
 }
 
 extern "C" int odin_moe_gate_up(const void* h, int h_dtype, long long h_stride, const void* w, int w_dtype, const int* ids,
-                                int T, int per, int ff, int d, int act, void* out, void* stream) {
+                                int T, int per, int ff, int d, int act, int gated, void* out, void* stream) {
     if (T <= 0 || per <= 0) return 0;
-    if (act != MOE_ACT_SILU && act != MOE_ACT_GELU_TANH) return ODIN_ERR_BAD_ARG;
+    if (act != MOE_ACT_SILU && act != MOE_ACT_GELU_TANH && act != MOE_ACT_RELU2) return ODIN_ERR_BAD_ARG;
     const size_t smem = (size_t)d * sizeof(float);
     if (smem > 200 * 1024 || (long long)T * per > 2147483647LL) return ODIN_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
@@ -221,7 +276,7 @@ extern "C" int odin_moe_gate_up(const void* h, int h_dtype, long long h_stride, 
         if (smem > 48 * 1024)                                                                                         \
             cudaFuncSetAttribute(moe_gate_up_kernel<TH, TW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
         odin_launch(moe_gate_up_kernel<TH, TW>, grid, dim3(MOE_THREADS), smem, s, (const TH*)h, (size_t)h_stride,     \
-                    (const TW*)w, ids, per, ff, d, act, (TH*)out);                                                    \
+                    (const TW*)w, ids, per, ff, d, act, gated, (TH*)out);                                             \
     } while (0)
     if (h_dtype == ODIN_BF16 && w_dtype == ODIN_BF16) GO(bf16, bf16);
     else if (h_dtype == ODIN_F32 && w_dtype == ODIN_F32) GO(float, float);

@@ -140,7 +140,7 @@ def cast(src: torch.Tensor, dst: torch.Tensor) -> None:
         c_longlong(src.numel()), _stream()), "cast")
 
 
-ACTIVATIONS = {"tanh": 0, "silu": 1, "gelu_tanh": 2, "xielu": 3}
+ACTIVATIONS = {"tanh": 0, "silu": 1, "gelu_tanh": 2, "xielu": 3, "relu2": 4}   # relu2: max(z, 0)^2
 
 
 def _parts(t: torch.Tensor, rows: int, cols: int) -> tuple[int, int]:
@@ -151,12 +151,13 @@ def _parts(t: torch.Tensor, rows: int, cols: int) -> tuple[int, int]:
 
 def row_update(x: torch.Tensor, delta, bias: torch.Tensor | None, weight: torch.Tensor | None,
                eps: float, groups: int, out: torch.Tensor | None, rows: torch.Tensor | None = None,
-               normalise: bool = True) -> None:
+               normalise: bool = True, scale: float = 1.0) -> None:
     """x += sum of delta's parts + bias (in place, 32-bit; not with a row gather), then
     normalise: out = weight * x / rms, the root mean square taken over each of `groups` equal
     consecutive parts of the row by itself (out may be x: in place); else out = x converted
     (out None: the update alone).  delta may be a list of up to three updates (each [n, d] or
-    [parts, n, d]; all but the first 32-bit), which are added in their order."""
+    [parts, n, d]; all but the first 32-bit), which are added in their order.  scale != 1: the updates (and the
+    bias) are added up by themselves and x += scale * their sum."""
     d = x.shape[-1]
     assert x.dtype == torch.float32 and x.is_contiguous()
     more = []
@@ -165,7 +166,7 @@ def row_update(x: torch.Tensor, delta, bias: torch.Tensor | None, weight: torch.
     n_split, stride = (1, 0)
     if delta is not None:
         n_split, stride = _parts(delta, x.shape[0], d)
-    if more:
+    if more or (scale != 1.0 and delta is not None):
         assert len(more) <= 2 and all(m.dtype == torch.float32 for m in more)
         extra = []
         for m in more + [None] * (2 - len(more)):
@@ -183,7 +184,7 @@ def row_update(x: torch.Tensor, delta, bias: torch.Tensor | None, weight: torch.
             _ptr(bias), c_int(dtype_code(bias.dtype) if bias is not None else 0), _ptr(weight),
             c_int(dtype_code(weight.dtype) if weight is not None else 0), c_float(eps), c_int(groups),
             c_int(0 if normalise else 1), _ptr(out), c_int(dtype_code(out.dtype) if out is not None else 0), _ptr(rows),
-            c_int(n_rows), c_int(d), _stream()), "row_update")
+            c_int(n_rows), c_int(d), c_float(scale), _stream()), "row_update")
         return
     if out is not None:
         assert out.is_contiguous() and out.shape[-1] == d
@@ -212,11 +213,15 @@ def normed_add(x: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: floa
         c_int(dtype_code(weight.dtype)), c_float(eps), _ptr(tok_seq), c_int(n), c_int(d), _stream()), "normed_add")
 
 
-def activation(src: torch.Tensor, kind: str, out: torch.Tensor, params: torch.Tensor | None = None) -> None:
+def activation(src: torch.Tensor, kind: str, out: torch.Tensor, params: torch.Tensor | None = None,
+               row_scale: torch.Tensor | None = None) -> None:
     """out = act(src) element by element; src [T, n] (a strided view is fine) or [parts, T, n] partial sums,
     added first.  kind: tanh, silu, gelu_tanh, or xielu with params = (p, q):
-    z > 0: softplus(p) z^2 + z/2, else (1/2 + softplus(q)) (e^z - 1 - z) + z/2."""
+    z > 0: softplus(p) z^2 + z/2, else (1/2 + softplus(q)) (e^z - 1 - z) + z/2; relu2: max(z, 0)^2.
+    row_scale: float32 [T]; row t of the result is multiplied by row_scale[t]."""
     T, n = out.shape
+    if row_scale is not None:
+        assert row_scale.dtype == torch.float32 and row_scale.is_contiguous() and row_scale.numel() == T
     assert out.stride(1) == 1 and src.stride(-1) == 1 and tuple(src.shape[-2:]) == (T, n)
     if src.dim() == 3:
         assert src.is_contiguous()
@@ -226,7 +231,7 @@ def activation(src: torch.Tensor, kind: str, out: torch.Tensor, params: torch.Te
     _check(_fn("rowwise", "odin_activation")(
         _ptr(src), c_int(dtype_code(src.dtype)), c_int(n_split), c_longlong(stride), c_longlong(row),
         c_int(ACTIVATIONS[kind]), _ptr(params), c_int(dtype_code(params.dtype) if params is not None else 0), _ptr(out),
-        c_int(dtype_code(out.dtype)), c_longlong(out.stride(0)), c_int(T), c_int(n), _stream()), "activation")
+        c_int(dtype_code(out.dtype)), c_longlong(out.stride(0)), c_int(T), c_int(n), _ptr(row_scale), _stream()), "activation")
 
 
 def gated_activation(gate_up: torch.Tensor, kind: str, out: torch.Tensor) -> None:
@@ -270,34 +275,50 @@ def softcap(z: torch.Tensor, cap: float) -> None:
 
 
 def moe_router(h: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None, top: int, always: int,
-               tok_seq: torch.Tensor | None, ids: torch.Tensor, wts: torch.Tensor, logits: torch.Tensor | None = None) -> None:
+               tok_seq: torch.Tensor | None, ids: torch.Tensor, wts: torch.Tensor, logits: torch.Tensor | None = None,
+               score: str = "softmax_of_chosen", groups: int = 1, keep: int = 1, route_scale: float = 1.0,
+               gate_row: bool = False, gate_out: torch.Tensor | None = None) -> None:
     """Per token: logits W h + bias in 32-bit, the `top` largest chosen, weights = softmax over the chosen logits;
     `always` further choices name the experts E, E + 1, ... with weight 1.  ids int32, wts float32: [T, top + always];
-    rows of sequence -1 get expert -1.  logits: W h where a product has formed it already (float32 [T, E])."""
+    rows of sequence -1 get expert -1.  logits: W h where a product has formed it already (float32 [T, rows of W]).
+
+    score "sigmoid_in_groups": scores sigmoid(z); the experts form `groups` equal groups of neighbours, a group's score
+    is the sum of its two largest scores, only experts of the `keep` best groups can be chosen (the `top` largest
+    scores among them); weights = chosen scores / (their sum + 1e-20) * route_scale.
+    gate_row: W has one row more than there are experts, g; the `always` choices are weighted by sigmoid(g . h),
+    which also goes to gate_out (float32 [T]) where given."""
     T, d = h.shape
-    E = w.shape[0]
+    E = w.shape[0] - (1 if gate_row else 0)
     assert h.stride(1) == 1 and w.is_contiguous() and w.shape[1] == d
     assert ids.dtype == torch.int32 and wts.dtype == torch.float32 and ids.is_contiguous() and wts.is_contiguous()
     assert tuple(ids.shape) == tuple(wts.shape) == (T, top + always)
     if bias is not None:
         assert bias.numel() == E and bias.is_contiguous()
     if logits is not None:
-        assert logits.dtype == torch.float32 and logits.is_contiguous() and tuple(logits.shape) == (T, E)
+        assert logits.dtype == torch.float32 and logits.is_contiguous() and tuple(logits.shape) == (T, w.shape[0])
+    if gate_out is not None:
+        assert gate_row and gate_out.dtype == torch.float32 and gate_out.is_contiguous() and gate_out.numel() == T
     _check(_fn("moe", "odin_moe_router")(
         _ptr(h), c_int(dtype_code(h.dtype)), c_longlong(h.stride(0)), _ptr(w), c_int(dtype_code(w.dtype)), _ptr(bias),
         c_int(dtype_code(bias.dtype) if bias is not None else 0), c_int(T), c_int(E), c_int(d), c_int(top), c_int(always),
-        _ptr(tok_seq), _ptr(ids), _ptr(wts), _ptr(logits), _stream()), "moe_router")
+        _ptr(tok_seq), _ptr(ids), _ptr(wts), _ptr(logits), c_int(ROUTER_SCORES[score]), c_int(groups), c_int(keep),
+        c_float(route_scale), c_int(1 if gate_row else 0), _ptr(gate_out), _stream()), "moe_router")
 
 
-def moe_gate_up(h: torch.Tensor, w: torch.Tensor, ids: torch.Tensor, kind: str, out: torch.Tensor) -> None:
-    """out[t * per + k, :] = act(Wg[e] h[t]) * (Wu[e] h[t]) with e = ids[t, k]; w: [experts, 2 ff, d], gate rows first."""
+ROUTER_SCORES = {"softmax_of_chosen": 0, "sigmoid_in_groups": 1}
+
+
+def moe_gate_up(h: torch.Tensor, w: torch.Tensor, ids: torch.Tensor, kind: str, out: torch.Tensor, gated: bool = True) -> None:
+    """out[t * per + k, :] = act(Wg[e] h[t]) * (Wu[e] h[t]) with e = ids[t, k]; w: [experts, 2 ff, d], gate rows first.
+    Not gated: out[t * per + k, :] = act(W[e] h[t]), w: [experts, ff, d]."""
     T, d = h.shape
     per, ff = ids.shape[1], out.shape[1]
-    assert h.stride(1) == 1 and w.is_contiguous() and tuple(w.shape[1:]) == (2 * ff, d) and out.is_contiguous()
+    assert h.stride(1) == 1 and w.is_contiguous() and tuple(w.shape[1:]) == ((2 if gated else 1) * ff, d) and out.is_contiguous()
     assert out.shape[0] == T * per and out.dtype == h.dtype and ids.dtype == torch.int32 and ids.is_contiguous()
     _check(_fn("moe", "odin_moe_gate_up")(
         _ptr(h), c_int(dtype_code(h.dtype)), c_longlong(h.stride(0)), _ptr(w), c_int(dtype_code(w.dtype)), _ptr(ids),
-        c_int(T), c_int(per), c_int(ff), c_int(d), c_int(ACTIVATIONS[kind]), _ptr(out), _stream()), "moe_gate_up")
+        c_int(T), c_int(per), c_int(ff), c_int(d), c_int(ACTIVATIONS[kind]), c_int(1 if gated else 0), _ptr(out),
+        _stream()), "moe_gate_up")
 
 
 def moe_down(a: torch.Tensor, w: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, out: torch.Tensor) -> None:
@@ -404,10 +425,10 @@ def token_shift(h: torch.Tensor, state: torch.Tensor, mu: torch.Tensor, out: tor
         c_int(T), c_int(d), _stream()), "token_shift")
 
 
-RECURRENCE_MODES = {"bonus": 0, "gated": 1}
+RECURRENCE_MODES = {"bonus": 0, "gated": 1, "fixed": 2}
 
 
-def linear_recurrence(mode: str, q: torch.Tensor, k: torch.Tensor | None, g: torch.Tensor, v: torch.Tensor,
+def linear_recurrence(mode: str, q: torch.Tensor, k: torch.Tensor | None, g: torch.Tensor | None, v: torch.Tensor,
                       c0: torch.Tensor, c1: torch.Tensor, out: torch.Tensor, state: torch.Tensor,
                       seq_start: torch.Tensor, seq_slots: torch.Tensor, n_seqs: int, n_heads: int, dk: int, dv: int,
                       shift_src: torch.Tensor | None = None, shift_state: torch.Tensor | None = None,
@@ -417,6 +438,7 @@ def linear_recurrence(mode: str, q: torch.Tensor, k: torch.Tensor | None, g: tor
 
     "bonus": w = exp(-exp(g + c0)); o = (S + diag(c1) k v^T)^T q; S = diag(w) S + k v^T
     "gated": f = c1 + (1 - c1) sigmoid(g + c0); S = diag(f) S + (1 - f) v^T; o = S^T silu(q)
+    "fixed": S = diag(c0) S + k v^T; o = S^T q (a constant decay per head and key channel; g and c1 unused)
 
     q, k, g: float32 [T, H dk] (strided views are fine), v, out: float32 [T, H dv].
     shift_src / shift_state: after the walk the last row of shift_src of every sequence is stored
@@ -426,6 +448,9 @@ def linear_recurrence(mode: str, q: torch.Tensor, k: torch.Tensor | None, g: tor
     of block_len tokens that are walked side by side from a state of zeros; two small kernels then carry the
     state from block to block and add each block's incoming state to its tokens' outputs.  The same values up
     to rounding (sums in another order); for long prompts, which one walk per head cannot fill the GPU with."""
+    if g is None:
+        assert mode == "fixed"
+        g = q
     for t in (q, g, v, out) + ((k,) if k is not None else ()):
         assert t.dtype == torch.float32 and t.stride(1) == 1
     assert state.dtype == torch.float32 and state.stride(1) == 1 and c0.dtype == c1.dtype
@@ -454,19 +479,88 @@ def linear_recurrence(mode: str, q: torch.Tensor, k: torch.Tensor | None, g: tor
         c_int(n_blocks), _ptr(qp), _ptr(s_loc), _ptr(d_tot), _stream()), "linear_recurrence", kernels=kernels)
 
 
-def head_unit_scale(o: torch.Tensor, weight: torch.Tensor, per_head_weight: bool, gate: torch.Tensor | None,
+def head_unit_scale(o: torch.Tensor, weight: torch.Tensor | None, per_head_weight: bool, gate: torch.Tensor | None,
                     eps: float, out: torch.Tensor, n_heads: int, dv: int) -> None:
     """out[t, h] = o[t, h] / rms(o[t, h]) * weight * silu(gate[t, h]) per head of dv elements; weight is
-    [H dv] (per_head_weight) or [dv] shared by the heads; gate (float32, optional) may be a strided view."""
+    [H dv] (per_head_weight) or [dv] shared by the heads, or None (no weight); gate (float32, optional) may be a
+    strided view."""
     T = o.shape[0]
     assert o.dtype == torch.float32 and o.is_contiguous() and out.is_contiguous() and tuple(out.shape) == (T, n_heads * dv)
-    assert weight.numel() == (n_heads * dv if per_head_weight else dv)
+    assert weight is None or weight.numel() == (n_heads * dv if per_head_weight else dv)
     if gate is not None:
         assert gate.dtype == torch.float32 and gate.stride(1) == 1
     _check(_fn("recurrent", "odin_head_unit_scale")(
-        _ptr(o), _ptr(weight), c_int(dtype_code(weight.dtype)), c_int(dv if per_head_weight else 0), _ptr(gate),
+        _ptr(o), _ptr(weight), c_int(dtype_code(weight.dtype) if weight is not None else 0),
+        c_int(dv if per_head_weight else 0), _ptr(gate),
         c_longlong(gate.stride(0) if gate is not None else 0), c_float(eps), _ptr(out), c_int(dtype_code(out.dtype)),
         c_int(T), c_int(n_heads), c_int(dv), _stream()), "head_unit_scale")
+
+
+def latent_prep(down: torch.Tensor, q_rank: int, kv_rank: int, rot: int, pairs: bool, q_norm: torch.Tensor | None,
+                c_norm: torch.Tensor, eps: float, cq: torch.Tensor | None, cos: torch.Tensor, sin: torch.Tensor,
+                tok_pos: torch.Tensor, tok_seq: torch.Tensor, block_table: torch.Tensor, cache: torch.Tensor | None,
+                write_cache: bool = True) -> None:
+    """A row of the fused down projection, down = [T, q_rank + kv_rank + rot] (or float32 partial sums [parts, T, ...]),
+    is [query latent | key/value latent | key part that is rotated]: cq [T, q_rank] = RMSNorm(query latent) * q_norm;
+    the cache row of the token's position, [kv_rank + rot] wide, becomes [RMSNorm(key/value latent) * c_norm | the key
+    part rotated by the position] (pairs: elements 2i with 2i + 1, else i with i + rot / 2).
+    cache: [pages, 1, PAGE, kv_rank + rot] of cq's type; cos, sin: float32 [positions, rot / 2]."""
+    n = q_rank + kv_rank + rot
+    if down.dim() == 3:
+        n_split, T = down.shape[0], down.shape[1]
+        assert down.is_contiguous() and down.shape[2] == n
+        split_stride, row_stride = T * n, n
+    else:
+        n_split, T, split_stride, row_stride = 1, down.shape[0], 0, down.stride(0)
+        assert down.stride(1) == 1 and down.shape[1] == n
+    out_dtype = cq.dtype if cq is not None else cache.dtype
+    if q_rank:
+        assert cq is not None and cq.is_contiguous() and tuple(cq.shape) == (T, q_rank) and q_norm.numel() == q_rank
+        assert q_norm.dtype == c_norm.dtype
+    assert c_norm.numel() == kv_rank and cos.dtype == sin.dtype == torch.float32 and cos.is_contiguous() and sin.is_contiguous()
+    assert rot == 0 or cos.shape[1] == rot // 2
+    if write_cache:
+        assert cache is not None and cache.is_contiguous() and cache.dtype == out_dtype
+        assert tuple(cache.shape[1:]) == (1, PAGE, kv_rank + rot), "the latent cache is [page][1][64][kv_rank + rot]"
+    _check(_fn("latent", "odin_latent_prep")(
+        _ptr(down), c_int(dtype_code(down.dtype)), c_int(n_split), c_longlong(split_stride), c_longlong(row_stride),
+        c_int(T), c_int(q_rank), c_int(kv_rank), c_int(rot), c_int(1 if pairs else 0), _ptr(q_norm), _ptr(c_norm),
+        c_int(dtype_code(c_norm.dtype)), c_float(eps), _ptr(cq), c_int(dtype_code(out_dtype)), _ptr(cos), _ptr(sin),
+        c_int(cos.shape[0]), _ptr(tok_pos), _ptr(tok_seq), _ptr(block_table), c_int(block_table.stride(0)), _ptr(cache),
+        c_int(PAGE), c_int(1 if write_cache else 0), _stream()), "latent_prep")
+
+
+def heads_linear(a: torch.Tensor, a_head_stride: int, w: torch.Tensor, out: torch.Tensor, out_head_stride: int) -> None:
+    """A product per head: out[t, h * out_head_stride + n] = sum_k a[t, h * a_head_stride + k] * w[h, k, n] for
+    w [H, K, N] (input channel before output channel); a and out may be views with any row stride."""
+    H, K, N = w.shape
+    T = a.shape[0]
+    assert w.is_contiguous() and a.stride(1) == 1 and out.stride(1) == 1 and out.shape[0] == T
+    assert a.shape[1] >= (H - 1) * a_head_stride + K and out.shape[1] >= (H - 1) * out_head_stride + N
+    _check(_fn("latent", "odin_heads_linear")(
+        _ptr(a), c_int(dtype_code(a.dtype)), c_longlong(a.stride(0)), c_longlong(a_head_stride), _ptr(w),
+        c_int(dtype_code(w.dtype)), _ptr(out), c_int(dtype_code(out.dtype)), c_longlong(out.stride(0)),
+        c_longlong(out_head_stride), c_int(T), c_int(H), c_int(N), c_int(K), _stream()), "heads_linear")
+
+
+def rope_heads(src: torch.Tensor, src_head_stride: int, dst: torch.Tensor, dst_head_stride: int, n_heads: int, width: int,
+               rot: int, pairs: bool, cos: torch.Tensor, sin: torch.Tensor, tok_pos: torch.Tensor, scale: float = 1.0,
+               scale_from_head: int | None = None) -> None:
+    """dst[t, h, :width] = src[t, h, :width] with the first `rot` elements of every head turned by tok_pos[t] (pairs:
+    element 2i with 2i + 1, else i with i + rot / 2) and the rest copied; heads from scale_from_head on are multiplied
+    by `scale`.  src and dst: views with any row stride, heads src_head_stride / dst_head_stride elements apart; they
+    may be the same memory."""
+    T = src.shape[0]
+    assert src.stride(1) == 1 and dst.stride(1) == 1 and dst.shape[0] == T
+    assert src.shape[1] >= (n_heads - 1) * src_head_stride + width and dst.shape[1] >= (n_heads - 1) * dst_head_stride + width
+    assert cos.dtype == sin.dtype == torch.float32 and cos.is_contiguous() and sin.is_contiguous()
+    assert rot == 0 or cos.shape[1] == rot // 2
+    _check(_fn("latent", "odin_rope_heads")(
+        _ptr(src), c_int(dtype_code(src.dtype)), c_longlong(src.stride(0)), c_longlong(src_head_stride), _ptr(dst),
+        c_int(dtype_code(dst.dtype)), c_longlong(dst.stride(0)), c_longlong(dst_head_stride), c_int(T), c_int(n_heads),
+        c_int(width), c_int(rot), c_int(1 if pairs else 0), c_float(scale),
+        c_int(n_heads if scale_from_head is None else scale_from_head), _ptr(cos), _ptr(sin), c_int(cos.shape[0]),
+        _ptr(tok_pos), _stream()), "rope_heads")
 
 
 def gemm_plain(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:

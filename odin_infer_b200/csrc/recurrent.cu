@@ -7,7 +7,8 @@
 //         o_t = (diag(a_t) S_(t-1) + diag(b) k_t v_t^T)^T q_t,   S_t = diag(w_t) S_(t-1) + k_t v_t^T,
 //     in its two uses: with a = 1 and a bonus b = u for the current token (output before the
 //     decay: the "wkv" form), and with a = w, b = 1 (output after the update: the gated form in
-//     which the forget gate f also scales what is written, k = 1 - f);
+//     which the forget gate f also scales what is written, k = 1 - f); and with a = w = one constant per head
+//     (retention: no gate, the keys and queries as they come, output after the update);
 //   * the per-head unit norm of the recurrence's output, times a weight, times an optional gate.
 //
 // The state lives in 32-bit floats in the engine's per-sequence state area and is carried from
@@ -76,6 +77,7 @@ extern "C" int odin_token_shift(const void* h, int dtype, const float* state, lo
 // ------------------------------------------------------------ the recurrence
 #define REC_BONUS 0   // o = (S + diag(u) k v^T)^T r, then S = diag(w) S + k v^T, w = exp(-exp(raw + w0))
 #define REC_GATED 1   // f = l + (1 - l) sigmoid(raw + b); S = diag(f) S + (1 - f) v^T; o = S^T silu(q)
+#define REC_FIXED 2   // S = diag(c0) S + k v^T; o = S^T q: a decay that is a constant per (head, key channel)
 // Threads that share a column of S: each owns a quarter of the key channels.  (Sixteen lanes per column, a quarter of
 // the registers each, walked a prompt of 2,048 tokens a fifth faster and made a decode step three to four times slower:
 // four times the threads for the same work.)
@@ -84,8 +86,8 @@ extern "C" int odin_token_shift(const void* h, int dtype, const float* state, lo
 
 struct RecParams {
     const float* q; long long q_stride;   // [rows, H*dk] projections (32-bit), row strides in elements
-    const float* k; long long k_stride;   // REC_BONUS only
-    const float* g; long long g_stride;   // the raw decay / forget gate
+    const float* k; long long k_stride;   // REC_BONUS and REC_FIXED
+    const float* g; long long g_stride;   // the raw decay / forget gate (REC_FIXED: unused)
     const float* v; long long v_stride;   // [rows, H*dv]
     VecRef c0, c1;                        // per (head, key channel): REC_BONUS w0 and u; REC_GATED bias and lower bound
     float* o; long long o_stride;         // [rows, H*dv]
@@ -169,8 +171,8 @@ linear_recurrence_kernel(RecParams p) {
                 if (i < dk) {
                     const size_t r = (size_t)(t0 + u);
                     rq[f] = p.q[r * p.q_stride + hc + i];
-                    rg[f] = p.g[r * p.g_stride + hc + i];
-                    if (MODE == REC_BONUS) rk[f] = p.k[r * p.k_stride + hc + i];
+                    if (MODE != REC_FIXED) rg[f] = p.g[r * p.g_stride + hc + i];
+                    if (MODE != REC_GATED) rk[f] = p.k[r * p.k_stride + hc + i];
                 }
             }
             if (e < nt * ccols) {
@@ -191,6 +193,10 @@ linear_recurrence_kernel(RecParams p) {
                         qv = rq[f];
                         kv = rk[f];
                         wv = expf(-expf(rg[f] + p.c0.at(hc + i)));
+                    } else if (MODE == REC_FIXED) {
+                        qv = rq[f];
+                        kv = rk[f];
+                        wv = p.c0.at(hc + i);
                     } else {
                         const float l = p.c1.at(hc + i);
                         const float fg = l + (1.0f - l) * (1.0f / (1.0f + expf(-(rg[f] + p.c0.at(hc + i)))));
@@ -228,7 +234,7 @@ linear_recurrence_kernel(RecParams p) {
                     if (BLOCKS) {
                         // q times the decays between the block's start and this token's look at the state:
                         // before its own decay where the output comes before the update, after it else
-                        if (MODE == REC_GATED) D[BLOCKS ? i : 0] *= ww[e];
+                        if (MODE != REC_BONUS) D[BLOCKS ? i : 0] *= ww[e];
                         if (writes_qp && i0 + i < dk)
                             p.qp[(size_t)(t0 + u) * p.H * dk + hc + i0 + i] = qq[e] * D[BLOCKS ? i : 0];
                         if (MODE == REC_BONUS) D[BLOCKS ? i : 0] *= ww[e];
@@ -341,7 +347,7 @@ extern "C" int odin_linear_recurrence(int mode, const float* q, long long q_stri
                                             (long long)n_seqs * n_blocks > 2147483647LL)))
         return ODIN_ERR_BAD_ARG;
     if (H <= 0 || dk <= 0 || dk > REC_MAX_DK || dv <= 0 || dv > 256 || H > 65535) return ODIN_ERR_UNSUPPORTED;
-    if (mode != REC_BONUS && mode != REC_GATED) return ODIN_ERR_BAD_ARG;
+    if (mode != REC_BONUS && mode != REC_GATED && mode != REC_FIXED) return ODIN_ERR_BAD_ARG;
     RecParams p;
     p.q = q; p.q_stride = q_stride; p.k = k; p.k_stride = k_stride; p.g = g; p.g_stride = g_stride;
     p.v = v; p.v_stride = v_stride;
@@ -368,6 +374,8 @@ extern "C" int odin_linear_recurrence(int mode, const float* q, long long q_stri
     do {                                                                                                        \
         if (mode == REC_BONUS && blocks) odin_launch(linear_recurrence_kernel<SL, REC_BONUS, true>, grid, dim3(threads), 0, s, p);  \
         else if (mode == REC_BONUS) odin_launch(linear_recurrence_kernel<SL, REC_BONUS, false>, grid, dim3(threads), 0, s, p);     \
+        else if (mode == REC_FIXED && blocks) odin_launch(linear_recurrence_kernel<SL, REC_FIXED, true>, grid, dim3(threads), 0, s, p);  \
+        else if (mode == REC_FIXED) odin_launch(linear_recurrence_kernel<SL, REC_FIXED, false>, grid, dim3(threads), 0, s, p);     \
         else if (blocks) odin_launch(linear_recurrence_kernel<SL, REC_GATED, true>, grid, dim3(threads), 0, s, p);  \
         else odin_launch(linear_recurrence_kernel<SL, REC_GATED, false>, grid, dim3(threads), 0, s, p);         \
     } while (0)
@@ -392,7 +400,7 @@ extern "C" int odin_linear_recurrence(int mode, const float* q, long long q_stri
 
 // ------------------------------------------------------------ per-head unit norm, weight, gate
 // out[t, h, :] = o[t, h, :] / sqrt(mean(o[t, h, :]^2) + eps) * w[h * w_head_stride + :] * silu(gate[t, h, :])
-// One warp per (token, head); the gate is optional.
+// One warp per (token, head); the gate and the weight are optional.
 template <typename TO>
 __global__ void __launch_bounds__(128)
 head_unit_scale_kernel(const float* __restrict__ o, const VecRef w, int w_head_stride, const float* __restrict__ gate,
@@ -412,7 +420,8 @@ head_unit_scale_kernel(const float* __restrict__ o, const VecRef w, int w_head_s
     const float rs = 1.0f / sqrtf(ss);
     TO* dst = out + ((size_t)t * H + h) * dv;
     for (int c = lane; c < dv; c += 32) {
-        float y = w.at(h * w_head_stride + c) * (rs * src[c]);
+        float y = rs * src[c];
+        if (w.p != nullptr) y = w.at(h * w_head_stride + c) * y;
         if (gate != nullptr) {
             const float z = gate[(size_t)t * gate_stride + (size_t)h * dv + c];
             y *= z / (1.0f + expf(-z));

@@ -21,10 +21,12 @@
 // VEC: the row, a group and every distance between rows and parts are multiples of four elements and every
 // pointer is 16-byte aligned, so everything moves four elements at a time; the same sums in the same order.
 // more: up to two further updates (32-bit, each with parts of its own), added after `delta` in their order.
+// scale != 1: the updates and the bias are added up by themselves first, and x_new = x + scale * their sum.
 struct MoreDeltas {
     const float* p[2];
     int n_split[2];
     long long stride[2];
+    float scale;
 };
 
 template <typename TD, typename TO, bool VEC>
@@ -47,9 +49,11 @@ row_update_kernel(float* x, const TD* __restrict__ delta, int n_split, size_t sp
     float* xr = x + (size_t)src * d;
     const bool updated = delta != nullptr || bias.p != nullptr || more.p[0] != nullptr || more.p[1] != nullptr;
     const bool write_back = updated && rows == nullptr;
+    const bool scaled = more.scale != 1.0f;
     if (VEC) {
         for (int j = threadIdx.x * 4; j < d; j += blockDim.x * 4) {
-            float4 v = ld4(xr + j);
+            const float4 x0 = ld4(xr + j);
+            float4 v = scaled ? make_float4(0.f, 0.f, 0.f, 0.f) : x0;
             if (delta != nullptr)
                 for (int s = 0; s < n_split; ++s) {
                     const float4 dv = ld4(delta + (size_t)s * split_stride + (size_t)src * d + j);
@@ -66,11 +70,14 @@ row_update_kernel(float* x, const TD* __restrict__ delta, int n_split, size_t sp
                 const float4 bv = bias.at4(j);
                 v.x += bv.x; v.y += bv.y; v.z += bv.z; v.w += bv.w;
             }
+            if (scaled) v = make_float4(fmaf(more.scale, v.x, x0.x), fmaf(more.scale, v.y, x0.y),
+                                        fmaf(more.scale, v.z, x0.z), fmaf(more.scale, v.w, x0.w));
             st4(rowbuf + j, v);
         }
     } else {
         for (int j = threadIdx.x; j < d; j += blockDim.x) {
-            float v = xr[j];
+            const float x0 = xr[j];
+            float v = scaled ? 0.f : x0;
             if (delta != nullptr)
                 for (int s = 0; s < n_split; ++s) v += to_f32(delta[(size_t)s * split_stride + (size_t)src * d + j]);
 #pragma unroll
@@ -78,6 +85,7 @@ row_update_kernel(float* x, const TD* __restrict__ delta, int n_split, size_t sp
                 if (more.p[m] != nullptr)
                     for (int s = 0; s < more.n_split[m]; ++s) v += more.p[m][(size_t)s * more.stride[m] + (size_t)src * d + j];
             if (bias.p != nullptr) v += bias.at(j);
+            if (scaled) v = fmaf(more.scale, v, x0);
             rowbuf[j] = v;
         }
     }
@@ -174,18 +182,19 @@ static int row_update_launch(float* x, const void* delta, int delta_dtype, int n
 extern "C" int odin_row_update(float* x, const void* delta, int delta_dtype, int n_split, long long split_stride,
                                const void* bias, int bias_dtype, const void* w, int w_dtype, float eps, int groups,
                                int mode, void* out, int out_dtype, const int* rows, int n_rows, int d, void* stream) {
-    MoreDeltas more{{nullptr, nullptr}, {0, 0}, {0, 0}};
+    MoreDeltas more{{nullptr, nullptr}, {0, 0}, {0, 0}, 1.0f};
     return row_update_launch(x, delta, delta_dtype, n_split, split_stride, bias, bias_dtype, w, w_dtype, eps, groups, mode,
                              out, out_dtype, rows, n_rows, d, more, stream);
 }
 
-// The same with up to two further 32-bit updates (null: none), each [parts][n, d], added after `delta`.
+// The same with up to two further 32-bit updates (null: none), each [parts][n, d], added after `delta`, and a factor
+// on the sum of all updates (x_new = x + scale * (updates + bias)).
 extern "C" int odin_row_update_several(float* x, const void* delta, int delta_dtype, int n_split, long long split_stride,
                                        const float* delta2, int n_split2, long long split_stride2, const float* delta3,
                                        int n_split3, long long split_stride3, const void* bias, int bias_dtype,
                                        const void* w, int w_dtype, float eps, int groups, int mode, void* out,
-                                       int out_dtype, const int* rows, int n_rows, int d, void* stream) {
-    MoreDeltas more{{delta2, delta3}, {n_split2, n_split3}, {split_stride2, split_stride3}};
+                                       int out_dtype, const int* rows, int n_rows, int d, float scale, void* stream) {
+    MoreDeltas more{{delta2, delta3}, {n_split2, n_split3}, {split_stride2, split_stride3}, scale};
     return row_update_launch(x, delta, delta_dtype, n_split, split_stride, bias, bias_dtype, w, w_dtype, eps, groups, mode,
                              out, out_dtype, rows, n_rows, d, more, stream);
 }
@@ -268,6 +277,7 @@ extern "C" int odin_normed_add(float* x, const void* y, int y_dtype, int n_split
 #define ACT_SILU 1
 #define ACT_GELU_TANH 2
 #define ACT_XIELU 3
+#define ACT_RELU2 4
 
 __device__ __forceinline__ float softplus_f(float z) { return fmaxf(z, 0.f) + log1pf(expf(-fabsf(z))); }
 
@@ -282,6 +292,7 @@ __device__ __forceinline__ float activate(int act, float z, float c0, float c1) 
         case ACT_TANH: return tanhf(z);
         case ACT_SILU: return z / (1.0f + expf(-z));
         case ACT_GELU_TANH: return gelu_tanh_f(z);
+        case ACT_RELU2: { const float r = fmaxf(z, 0.f); return r * r; }
         default: return z > 0.f ? c0 * z * z + 0.5f * z : c1 * (expm1f(z) - z) + 0.5f * z;
     }
 }
@@ -289,7 +300,7 @@ __device__ __forceinline__ float activate(int act, float z, float c0, float c1) 
 template <typename TI, typename TO, bool VEC>
 __global__ void __launch_bounds__(256)
 activation_kernel(const TI* __restrict__ in, int n_split, size_t split_stride, size_t in_stride, int act, VecRef params,
-                  TO* __restrict__ out, size_t out_stride, int T, int n) {
+                  TO* __restrict__ out, size_t out_stride, int T, int n, const float* __restrict__ row_scale) {
     pdl_trigger();
     float c0 = 0.f, c1 = 0.f;
     if (act == ACT_XIELU) {
@@ -307,8 +318,9 @@ activation_kernel(const TI* __restrict__ in, int n_split, size_t split_stride, s
                 const float4 v = ld4(in + (size_t)s * split_stride + (size_t)t * in_stride + c);
                 z.x += v.x; z.y += v.y; z.z += v.z; z.w += v.w;
             }
-            st4(out + (size_t)t * out_stride + c, make_float4(activate(act, z.x, c0, c1), activate(act, z.y, c0, c1),
-                                                               activate(act, z.z, c0, c1), activate(act, z.w, c0, c1)));
+            const float f = row_scale != nullptr ? row_scale[t] : 1.0f;
+            st4(out + (size_t)t * out_stride + c, make_float4(activate(act, z.x, c0, c1) * f, activate(act, z.y, c0, c1) * f,
+                                                               activate(act, z.z, c0, c1) * f, activate(act, z.w, c0, c1) * f));
         }
         return;
     }
@@ -317,15 +329,15 @@ activation_kernel(const TI* __restrict__ in, int n_split, size_t split_stride, s
         const int t = (int)(i / n), c = (int)(i % n);
         float z = 0.f;
         for (int s = 0; s < n_split; ++s) z += to_f32(in[(size_t)s * split_stride + (size_t)t * in_stride + c]);
-        out[(size_t)t * out_stride + c] = from_f32<TO>(activate(act, z, c0, c1));
+        out[(size_t)t * out_stride + c] = from_f32<TO>(activate(act, z, c0, c1) * (row_scale != nullptr ? row_scale[t] : 1.0f));
     }
 }
 
 extern "C" int odin_activation(const void* in, int in_dtype, int n_split, long long split_stride, long long in_stride,
                                int act, const void* params, int params_dtype, void* out, int out_dtype,
-                               long long out_stride, int T, int n, void* stream) {
+                               long long out_stride, int T, int n, const float* row_scale, void* stream) {
     if (T <= 0 || n <= 0) return 0;
-    if (act < 0 || act > ACT_XIELU || (act == ACT_XIELU && params == nullptr)) return ODIN_ERR_BAD_ARG;
+    if (act < 0 || act > ACT_RELU2 || (act == ACT_XIELU && params == nullptr)) return ODIN_ERR_BAD_ARG;
     cudaStream_t s = (cudaStream_t)stream;
     const bool vec = (n % 4 == 0) && (in_stride % 4 == 0) && (out_stride % 4 == 0) && (split_stride % 4 == 0) &&
                      ((((uintptr_t)in) | ((uintptr_t)out)) % 16 == 0);
@@ -336,7 +348,8 @@ extern "C" int odin_activation(const void* in, int in_dtype, int n_split, long l
     do {                                                                                                        \
         auto kern = vec ? activation_kernel<TI, TO, true> : activation_kernel<TI, TO, false>;                   \
         odin_launch(kern, dim3(blocks), dim3(256), 0, s, (const TI*)in, n_split,                                \
-                    (size_t)split_stride, (size_t)in_stride, act, pv, (TO*)out, (size_t)out_stride, T, n);      \
+                    (size_t)split_stride, (size_t)in_stride, act, pv, (TO*)out, (size_t)out_stride, T, n,       \
+                    row_scale);                                                                                 \
     } while (0)
     if (in_dtype == ODIN_F32 && out_dtype == ODIN_F32) GO(float, float);
     else if (in_dtype == ODIN_F32 && out_dtype == ODIN_BF16) GO(float, bf16);

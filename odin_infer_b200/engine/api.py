@@ -89,9 +89,10 @@ class Engine:
         self.cache_bytes = 0
         for g in self.cache.groups.values():
             k = torch.empty(g.storage_shape(), dtype=self.rt.dtype, device=self.rt.device)
-            v = torch.empty(g.value_storage_shape(), dtype=self.rt.dtype, device=self.rt.device)
+            shared = g.request.shared_kv   # one row per token is key and value: no second tensor
+            v = k if shared else torch.empty(g.value_storage_shape(), dtype=self.rt.dtype, device=self.rt.device)
             g.attach_storage(k, v)
-            self.cache_bytes += (k.numel() + v.numel()) * itemsize
+            self.cache_bytes += (k.numel() + (0 if shared else v.numel())) * itemsize
         nstate = self.cache.state_bytes_per_slot
         self.cache.state = torch.zeros(self.cache.max_slots, nstate, dtype=torch.uint8, device=self.rt.device)
         self.cache.zero_state = (lambda slot: self.cache.state[slot].zero_()) if nstate else None

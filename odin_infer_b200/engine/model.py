@@ -4,7 +4,7 @@ from __future__ import annotations
 
 import torch
 
-from ..parts.base import ParamSpec, build_part, split_update
+from ..parts.base import ParamSpec, build_part, split_update, update_factor
 from ..parts.spec import ModelSpec
 
 
@@ -24,7 +24,11 @@ class DecoderModel:
             if name is not None:
                 if name not in self.position_encodings:
                     raise ValueError(f"a mixer asks for position encoding '{name}', which the model does not define")
-                blk.mixer.pe = self.position_encodings[name]
+                pe = self.position_encodings[name]
+                layout = getattr(pe, "layout", "halves")
+                if layout not in getattr(blk.mixer, "rope_layouts", ("halves",)):
+                    raise ValueError(f"{type(blk.mixer).__name__} does not rotate in the '{layout}' layout of encoding '{name}'")
+                blk.mixer.pe = pe
 
     def _all_parts(self):
         return [self.embedding, *self.position_encodings.values(), *self.layers, self.final_norm, self.head]
@@ -98,8 +102,12 @@ class DecoderModel:
         if step.n_logit_rows == 0:
             return None
         delta, bias = split_update(pending)
-        if bias is None:
-            h = self.final_norm.forward(rt, x, delta, rows=step.logit_rows)
-        else:
-            h = self.final_norm.forward(rt, x, delta, rows=step.logit_rows, bias=bias)
+        more = {}
+        if update_factor(pending) != 1.0:
+            if not self.final_norm.takes_scale:
+                raise TypeError(f"{type(self.final_norm).__name__} follows a block whose update carries a factor, and takes none")
+            more["scale"] = update_factor(pending)
+        if bias is not None:
+            more["bias"] = bias
+        h = self.final_norm.forward(rt, x, delta, rows=step.logit_rows, **more)
         return self.head.forward(rt, step, h)

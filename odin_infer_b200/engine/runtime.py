@@ -225,11 +225,12 @@ class Runtime:
 
     # ---- experts chosen per token ----------------------------------------
     def experts(self, h: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, ids: torch.Tensor,
-                wts: torch.Tensor, activation: str) -> torch.Tensor:
+                wts: torch.Tensor, activation: str, gated: bool = True) -> torch.Tensor:
         """The chosen experts' gated feed-forwards for every (token, choice): ids / wts [T, per] name each
         choice's expert (-1: none) and weight; w_gate_up [experts, 2 inner, width], w_down [experts, width,
         inner].  Returns the tokens' update: float32 [per, T, width] partial sums (slice k holds every token's
-        k-th choice, weighted) from the row-by-row kernels, or float32 [T, width] from the grouped products."""
+        k-th choice, weighted) from the row-by-row kernels, or float32 [T, width] from the grouped products.
+        gated=False: an expert is W_down act(W_up h) and w_gate_up is [experts, inner, width]."""
         T, per = ids.shape
         inner, width = w_down.shape[2], w_down.shape[1]
         if T * per >= MOE_GROUPED_FROM_ROWS and ops.moe_grouped_supported(h, w_gate_up, w_down) and width % 4 == 0:
@@ -244,14 +245,19 @@ class Runtime:
             hs = self.empty(places, h.shape[1])
             ops.moe_gather(h, row_of_place, per, hs)
             a = self.empty(places, inner)
-            ops.moe_grouped(hs, w_gate_up, tile_expert, a, activation)
+            if gated:
+                ops.moe_grouped(hs, w_gate_up, tile_expert, a, activation)
+            else:
+                u = self.empty(places, inner, dtype=torch.float32)
+                ops.moe_grouped(hs, w_gate_up, tile_expert, u)
+                ops.activation(u, activation, a)
             c = self.empty(places, width, dtype=torch.float32)
             ops.moe_grouped(a, w_down, tile_expert, c)
             y = self.empty(T, width, dtype=torch.float32)
             ops.moe_combine(c, place_of_row, wts, y)
             return y
         a = self.empty(T * per, inner)
-        ops.moe_gate_up(h, w_gate_up, ids, activation, a)
+        ops.moe_gate_up(h, w_gate_up, ids, activation, a, gated=gated)
         y = self.empty(per, T, width, dtype=torch.float32)
         ops.moe_down(a, w_down, ids, wts, y)
         return y

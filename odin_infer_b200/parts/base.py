@@ -117,10 +117,26 @@ class Several(list):
     norm that says `takes_several` may follow; it gets them as a list in place of `delta`."""
 
 
+class Scaled:
+    """Updates of the residual stream that are to be added times a factor: x += factor * (sum of the updates).
+    `update`: what a mixer or feed-forward answers (a tensor, `Several`, `Biased`, None).  Only a norm that says
+    `takes_scale` may follow; it gets the factor as the keyword `scale=`."""
+
+    def __init__(self, update, factor: float):
+        self.update, self.factor = update, float(factor)
+
+
+def update_factor(pending) -> float:
+    """The factor on a pending update (1 unless it is `Scaled`)."""
+    return pending.factor if isinstance(pending, Scaled) else 1.0
+
+
 def split_update(pending):
     """(delta, bias) of what a mixer or feed-forward answered: each a tensor or None (delta a list of
-    tensors for `Several`)."""
+    tensors for `Several`).  The factor of a `Scaled` update is asked for with `update_factor`."""
     bias = None
+    if isinstance(pending, Scaled):
+        pending = pending.update
     if isinstance(pending, Biased):
         pending, bias = pending.update, pending.bias
     if isinstance(pending, ResidualAdded):
@@ -142,6 +158,7 @@ class Norm(Part):
 
     takes_bias = False
     takes_several = False   # `delta` may be a list of up to three updates
+    takes_scale = False     # takes a keyword `scale=`: x += scale * (the updates)
 
 
 class PositionEncoding(Part):

@@ -1,7 +1,7 @@
 """How a layer's parts are arranged."""
 from __future__ import annotations
 
-from .base import Block, PartSpec, ResidualAdded, Several, build_part, register_part, split_update
+from .base import Block, PartSpec, ResidualAdded, Scaled, Several, build_part, register_part, split_update, update_factor
 
 
 @register_part("block", "prenorm")
@@ -50,11 +50,17 @@ class PreNormBlock(Block):
     @staticmethod
     def _norm(norm, rt, x, pending):
         delta, bias = split_update(pending)
+        more = {}
+        factor = update_factor(pending)
+        if factor != 1.0:
+            if not norm.takes_scale:
+                raise TypeError(f"{type(norm).__name__} follows a block whose update carries a factor, and takes none")
+            more["scale"] = factor
         if bias is None:
-            return norm.forward(rt, x, delta)
+            return norm.forward(rt, x, delta, **more)
         if not norm.takes_bias:
             raise TypeError(f"{type(norm).__name__} follows a part whose update carries a bias, and takes none")
-        return norm.forward(rt, x, delta, bias=bias)
+        return norm.forward(rt, x, delta, bias=bias, **more)
 
     def forward(self, rt, step, x, pending, entry):
         mixer, ffn = self._mixer, self.ffn
@@ -65,6 +71,8 @@ class PreNormBlock(Block):
             pending = ffn.forward(rt, step, h, residual=x) if ffn.takes_residual else ffn.forward(rt, step, h)
         for extra in self.extras:
             x, pending = extra.forward(rt, step, x, pending)
+        if isinstance(pending, Scaled):
+            return x, pending
         delta, bias = split_update(pending)
         return x, (pending if bias is not None else delta)
 
@@ -74,29 +82,40 @@ class ParallelBlock(PreNormBlock):
     """h = Norm(x);  x -> x + Mixer(h) + FeedForward(h): one norm, and both sublayers read its output.
     A block may have no feed-forward.
 
+    norm_feed_forward: a second norm of the same x for the feed-forward, x -> x + Mixer(Norm1(x)) + FeedForward(Norm2(x)).
+    residual_mult m: x -> x + m * (Mixer(..) + FeedForward(..)); the factor travels with the pending updates (`Scaled`)
+    to the norm that adds them, and no product adds itself to x in its epilogue.
+
     Both updates stay pending (`Several`) and are added, in the order mixer, feed-forward, by the norm
     that runs next; a sublayer whose last product has added itself to x in its epilogue leaves nothing."""
 
-    def __init__(self, mixer: PartSpec, feed_forward: PartSpec | None, norm: PartSpec):
+    def __init__(self, mixer: PartSpec, feed_forward: PartSpec | None, norm: PartSpec,
+                 norm_feed_forward: PartSpec | None = None, residual_mult: float = 1.0):
         self._mixer = build_part("mixer", mixer)
         self.ffn = build_part("feed_forward", feed_forward) if feed_forward is not None else None
         self.norm_mixer = build_part("norm", norm)
-        self.norm_ffn = None
+        self.norm_ffn = build_part("norm", norm_feed_forward) if (norm_feed_forward is not None and self.ffn is not None) else None
         self.extras = []
+        self.residual_mult = float(residual_mult)
         if not self.norm_mixer.takes_several:
             raise TypeError(f"{type(self.norm_mixer).__name__} cannot add several pending updates")
 
     def forward(self, rt, step, x, pending, entry):
         mixer, ffn = self._mixer, self.ffn
+        plain = self.residual_mult == 1.0   # else nothing may add itself to x unscaled
         h = self._norm(self.norm_mixer, rt, x, pending)
+        # x holds everything before this block now; a second norm reads the same x
+        h2 = h if self.norm_ffn is None else self.norm_ffn.forward(rt, x, None)
         # h is computed: a product that adds to x in its epilogue no longer changes what the sublayers read
-        out = [mixer.forward(rt, step, h, entry, residual=x) if mixer.takes_residual else mixer.forward(rt, step, h, entry)]
+        out = [mixer.forward(rt, step, h, entry, residual=x) if (mixer.takes_residual and plain) else mixer.forward(rt, step, h, entry)]
         if ffn is not None:
-            out.append(ffn.forward(rt, step, h, residual=x) if ffn.takes_residual else ffn.forward(rt, step, h))
+            out.append(ffn.forward(rt, step, h2, residual=x) if (ffn.takes_residual and plain) else ffn.forward(rt, step, h2))
         pending = Several()
         for upd in out:
             if isinstance(upd, Several):
                 pending.extend(upd)
             elif not isinstance(upd, ResidualAdded):
                 pending.append(upd)
-        return x, (pending if pending else None)
+        if not pending:
+            return x, None
+        return x, (pending if plain else Scaled(pending, self.residual_mult))

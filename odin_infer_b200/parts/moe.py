@@ -22,25 +22,49 @@ class RoutedExperts(FeedForward):
     uses with weight 1 (a gated feed-forward is a sum over its inner columns) and rides in the same launches;
     any other shared expert runs as a dense gated feed-forward beside them.
 
+    gated=False: an expert is W_down act(W_up h) (no gate matrix; names "up" / "down", "shared_up" / "shared_down");
+    activation may then also be "relu2", max(z, 0)^2.
+    score: how the router chooses and weighs: "softmax_of_chosen" as above, or "sigmoid_in_groups": scores
+    sigmoid(z) (no bias); the experts form `groups` equal groups of neighbours, a group's score is the sum of its
+    two largest scores, only experts of the `keep` best groups can be chosen, the `top` largest scores among them
+    are, and their weights are the scores divided by their sum (+ 1e-20), times `route_scale`.
+    shared_gate: the shared expert's output is multiplied by sigmoid(g . h), one number per token, g the tensor
+    names["shared_token_gate"] ([1, width]); g rides as one more row of the router's matrix.
+
     The update of few tokens comes back as partial sums, one slice per choice, which the next norm adds in order;
     with many tokens the rows are sorted by expert and run as grouped tensor-core products (`Runtime.experts`)."""
 
     graph_safe = True
 
     def __init__(self, width: int, inner: int, n_experts: int, top: int, names: dict, activation: str = "silu",
-                 shared_inner: int = 0):
+                 shared_inner: int = 0, gated: bool = True, score: str = "softmax_of_chosen", groups: int = 1,
+                 keep: int = 1, route_scale: float = 1.0, shared_gate: bool = False):
         if not (0 < top <= n_experts):
             raise ValueError(f"every token uses {top} of {n_experts} experts: not possible")
-        if activation not in ("silu", "gelu_tanh"):
-            raise ValueError(f"an expert's activation is silu or gelu_tanh, got '{activation}'")
+        if activation not in (("silu", "gelu_tanh") if gated else ("silu", "gelu_tanh", "relu2")):
+            raise ValueError(f"an expert's activation is silu or gelu_tanh (or relu2 without a gate), got '{activation}'")
+        if score not in ops.ROUTER_SCORES:
+            raise ValueError(f"a router scores by one of {', '.join(ops.ROUTER_SCORES)}, got '{score}'")
+        if groups < 1 or n_experts % groups or not (1 <= keep <= groups) or keep * (n_experts // groups) < top:
+            raise ValueError(f"{n_experts} experts in {groups} groups of which {keep} stay cannot give {top} experts a token")
+        if groups > 1 and score != "sigmoid_in_groups":
+            raise ValueError("groups of experts go with the score 'sigmoid_in_groups'")
+        if shared_gate and not shared_inner:
+            raise ValueError("a gate on the shared expert needs a shared expert")
+        if shared_gate and gated:
+            raise ValueError("a gate on the shared expert is built for experts without a gate matrix")
         self.width, self.inner, self.n_experts, self.top = width, inner, n_experts, top
         self.names, self.activation, self.shared_inner = dict(names), activation, int(shared_inner)
+        self.gated, self.score, self.groups, self.keep = bool(gated), score, int(groups), int(keep)
+        self.route_scale, self.shared_gate = float(route_scale), bool(shared_gate)
         # the shared expert as experts of the common size that every token uses
         self.shared_as_experts = self.shared_inner // inner if (self.shared_inner and self.shared_inner % inner == 0) else 0
         self.w_router = self.b_router = self.w_gate_up = self.w_down = self.ws_gate_up = self.ws_down = None
 
     def _expert_names(self, e: int):
         n = self.names
+        if not self.gated:
+            return n["up"].format(e=e), n["down"].format(e=e)
         return n["gate"].format(e=e), n["up"].format(e=e), n["down"].format(e=e)
 
     def params(self):
@@ -49,31 +73,43 @@ class RoutedExperts(FeedForward):
         if n.get("router_bias"):
             out.append(ParamSpec(n["router_bias"], (self.n_experts,), init="near_zero"))
         for e in range(self.n_experts):
-            g, u, d = self._expert_names(e)
-            out += [ParamSpec(g, (self.inner, self.width)), ParamSpec(u, (self.inner, self.width)),
-                    ParamSpec(d, (self.width, self.inner))]
+            *ups, d = self._expert_names(e)
+            out += [ParamSpec(u, (self.inner, self.width)) for u in ups] + [ParamSpec(d, (self.width, self.inner))]
         if self.shared_inner:
-            out += [ParamSpec(n["shared_gate"], (self.shared_inner, self.width)),
-                    ParamSpec(n["shared_up"], (self.shared_inner, self.width)),
+            if self.gated:
+                out.append(ParamSpec(n["shared_gate"], (self.shared_inner, self.width)))
+            out += [ParamSpec(n["shared_up"], (self.shared_inner, self.width)),
                     ParamSpec(n["shared_down"], (self.width, self.shared_inner))]
+            if self.shared_gate:
+                out.append(ParamSpec(n["shared_token_gate"], (1, self.width)))
         return out
 
     def bind(self, tensors, rt):
         n = self.names
         self.w_router = tensors[n["router"]].contiguous()
+        if self.shared_gate:
+            sg = tensors.pop(n["shared_token_gate"]).reshape(1, self.width)
+            wr = self.w_router
+            if sg.dtype != wr.dtype:
+                sg, wr = sg.float(), wr.float()
+            self.w_router = torch.cat([wr, sg], dim=0).contiguous()   # the gate's vector as the row after the experts'
         self.b_router = tensors[n["router_bias"]].to(torch.float32).contiguous() if n.get("router_bias") else None
         gate_up, down = [], []
         for e in range(self.n_experts):
-            g, u, d = (tensors.pop(k) for k in self._expert_names(e))
-            gate_up.append(torch.cat([g, u], dim=0))
+            *ups, d = (tensors.pop(k) for k in self._expert_names(e))
+            gate_up.append(torch.cat(ups, dim=0) if self.gated else ups[0])
             down.append(d)
         if self.shared_inner:
-            g, u, d = tensors.pop(n["shared_gate"]), tensors.pop(n["shared_up"]), tensors.pop(n["shared_down"])
+            g = tensors.pop(n["shared_gate"]) if self.gated else None
+            u, d = tensors.pop(n["shared_up"]), tensors.pop(n["shared_down"])
             if self.shared_as_experts:
                 f = self.inner
                 for p in range(self.shared_as_experts):
-                    gate_up.append(torch.cat([g[p * f:(p + 1) * f], u[p * f:(p + 1) * f]], dim=0))
+                    rows = [t[p * f:(p + 1) * f] for t in ((g, u) if self.gated else (u,))]
+                    gate_up.append(torch.cat(rows, dim=0) if self.gated else rows[0])
                     down.append(d[:, p * f:(p + 1) * f])
+            elif not self.gated:
+                self.ws_gate_up, self.ws_down = u.contiguous(), d
             else:
                 if g.dtype != u.dtype:
                     g, u = g.float(), u.float()
@@ -96,9 +132,18 @@ class RoutedExperts(FeedForward):
             # many tokens: the logits as a tensor-core product (bfloat16 factors, 32-bit sums); the 32-bit engine keeps
             # the one kernel whatever the number of tokens, so that a token's logits are the same bits in every cut
             logits = rt.linear(h, self.w_router, out_dtype=torch.float32)
-        ops.moe_router(h, self.w_router, self.b_router, self.top, self.shared_as_experts, step.tok_seq, ids, wts, logits)
-        y = rt.experts(h, self.w_gate_up, self.w_down, ids, wts, self.activation)
-        if self.ws_gate_up is None:
+        beside = self.ws_gate_up is not None   # a shared expert that runs as a dense feed-forward beside the experts
+        gate = rt.empty(T, dtype=torch.float32) if (self.shared_gate and beside) else None
+        ops.moe_router(h, self.w_router, self.b_router, self.top, self.shared_as_experts, step.tok_seq, ids, wts, logits,
+                       score=self.score, groups=self.groups, keep=self.keep, route_scale=self.route_scale,
+                       gate_row=self.shared_gate, gate_out=gate)
+        y = rt.experts(h, self.w_gate_up, self.w_down, ids, wts, self.activation, gated=self.gated)
+        if not beside:
             return y
-        act = rt.gated_linear(h, self.ws_gate_up, self.shared_inner, self.activation)
+        if self.gated:
+            act = rt.gated_linear(h, self.ws_gate_up, self.shared_inner, self.activation)
+        else:
+            # act(W_up h), every row times its token's gate: W_down (s a) = s (W_down a)
+            act = rt.empty(T, self.shared_inner)
+            ops.activation(rt.linear(h, self.ws_gate_up, may_split=True), self.activation, act, row_scale=gate)
         return Several([y, rt.linear(act, self.ws_down, out_dtype=torch.float32, may_split=True)])

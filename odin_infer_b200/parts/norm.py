@@ -19,6 +19,7 @@ class RMSNorm(Norm):
     graph_safe = True
     takes_bias = True
     takes_several = True
+    takes_scale = True
 
     def __init__(self, width: int, eps: float, weight: str, groups: int = 1, one_plus: bool = False):
         if groups < 1 or width % groups:
@@ -38,15 +39,17 @@ class RMSNorm(Norm):
     def kernel_groups(self):
         return {"elementwise", "rowwise"}
 
-    def forward(self, rt, x, delta, rows=None, bias=None):
+    def forward(self, rt, x, delta, rows=None, bias=None, scale: float = 1.0):
         n = x.shape[0] if rows is None else rows.numel()
         out = rt.empty(n, self.width)
         if isinstance(delta, (list, tuple)) and len(delta) == 1:
             delta = delta[0]
-        if self.groups == 1 and bias is None and not isinstance(delta, (list, tuple)):
+        if delta is None and bias is None:
+            scale = 1.0
+        if self.groups == 1 and bias is None and scale == 1.0 and not isinstance(delta, (list, tuple)):
             ops.add_rmsnorm(x, delta, self.weight, self.eps, out, rows)
         else:
-            ops.row_update(x, delta, bias, self.weight, self.eps, self.groups, out, rows)
+            ops.row_update(x, delta, bias, self.weight, self.eps, self.groups, out, rows, scale=scale)
         return out
 
     def in_place(self, rt, x) -> None:

@@ -103,6 +103,75 @@ class TokenShiftWKV(Mixer):
         return rt.linear(y, self.w["o"], out_dtype=torch.float32, may_split=True, add_to=residual)
 
 
+@register_part("mixer", "retention")
+class Retention(Mixer):
+    """Linear attention with one fixed decay per head, no softmax and no denominator.
+
+    q = W_q h, k = W_k h (heads x head_dim), v = W_v h (heads x v_head_dim), no biases; q and k are rotated by the
+    position (the encoding's first rotary_dim elements of a head, in its layout), then k is multiplied by
+    head_dim^(-1/2).  Per head, with the state S (head_dim x v_head_dim) zero at a sequence's start:
+
+        S_t = decay_h S_(t-1) + k_t v_t^T          o_t = S_t^T q_t
+
+    Each head's o is divided by its root mean square (no weight); the heads, side by side, are multiplied by
+    silu(W_g h) and go through W_o.  The four projections of h are fused into one at load and leave it as 32-bit;
+    rotation, scaling, decay and state are 32-bit.  names: "q", "k", "v", "g", "o"."""
+
+    graph_safe = True
+    rope_layouts = ("halves", "pairs")
+
+    def __init__(self, width: int, n_heads: int, head_dim: int, v_head_dim: int, decay, names: dict,
+                 position_encoding: str | None = None, eps: float = 1e-5):
+        decay = [float(d) for d in decay]
+        if len(decay) != n_heads:
+            raise ValueError(f"{n_heads} heads need as many decays, got {len(decay)}")
+        self.width, self.H, self.D, self.V, self.eps = width, n_heads, head_dim, v_head_dim, float(eps)
+        self.decay_values, self.names, self.pe_name = decay, dict(names), position_encoding
+        self.pe = None
+
+    def params(self):
+        n, qk, vv = self.names, self.H * self.D, self.H * self.V
+        return [ParamSpec(n["q"], (qk, self.width)), ParamSpec(n["k"], (qk, self.width)),
+                ParamSpec(n["v"], (vv, self.width)), ParamSpec(n["g"], (vv, self.width)),
+                ParamSpec(n["o"], (self.width, vv))]
+
+    def bind(self, tensors, rt):
+        n = self.names
+        mats = [tensors.pop(n[s]) for s in ("q", "k", "v", "g")]
+        if len({t.dtype for t in mats}) > 1:
+            mats = [t.float() for t in mats]
+        self.w_qkvg = torch.cat(mats, dim=0).contiguous()
+        self.w_o = tensors[n["o"]]
+        # the decay of every (head, key channel), rounded to 32-bit once
+        self.decay = torch.tensor(self.decay_values, dtype=torch.float64).to(torch.float32).repeat_interleave(self.D) \
+            .contiguous().to(rt.device)
+        self._dummy = torch.zeros(1, 1, dtype=torch.float32, device=rt.device)
+
+    def state_bytes(self) -> int:
+        return 4 * self.H * self.D * self.V
+
+    def kernel_groups(self):
+        return {"recurrent", "latent", "gemm_plain"}
+
+    def forward(self, rt, step, h, entry):
+        T, qk, vv = h.shape[0], self.H * self.D, self.H * self.V
+        qkvg = rt.linear(h, self.w_qkvg, out_dtype=torch.float32)
+        rot = self.pe.rotation() if self.pe is not None else None
+        cos, sin, rot_dim = rot if rot is not None else (self._dummy, self._dummy, 0)
+        pairs = rot is not None and self.pe.layout == "pairs"
+        # q and k are 2 H heads side by side: all are rotated in place, the k heads are scaled afterwards
+        both = qkvg[:, :2 * qk]
+        ops.rope_heads(both, self.D, both, self.D, 2 * self.H, self.D, rot_dim, pairs, cos, sin, step.tok_pos,
+                       scale=float(self.D) ** -0.5, scale_from_head=self.H)
+        o = rt.empty(T, vv, dtype=torch.float32)
+        ops.linear_recurrence("fixed", qkvg[:, :qk], qkvg[:, qk:2 * qk], None, qkvg[:, 2 * qk:2 * qk + vv], self.decay,
+                              self.decay, o, _f32_view(step.state(entry)), step.seq_start, step.seq_slots, step.n_seq_cap,
+                              self.H, self.D, self.V, block_len=_block_len(step), max_new=step.max_new)
+        y = rt.empty(T, vv)
+        ops.head_unit_scale(o, None, False, qkvg[:, 2 * qk + vv:], self.eps, y, self.H, self.V)
+        return rt.linear(y, self.w_o, out_dtype=torch.float32, may_split=True)
+
+
 @register_part("mixer", "gated_linear_recurrence")
 class GatedLinearRecurrence(Mixer):
     """Linear attention whose forget gate also decides what is written (the HGRN2 form).
