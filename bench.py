@@ -678,6 +678,235 @@ def nufupel_workload(steps: int, warmup: int) -> int:
     return 0
 
 
+# --------------------------------------------------------------------------------------------------------------
+# --workload nikonex: the Nikonex design beside the Nufupel design (the closest: parallel blocks, windows, experts)
+# --------------------------------------------------------------------------------------------------------------
+NIKONEX_SIZES = {
+    # the Nufupel sizes' width, experts, layers and vocabulary; latent attention whose cached row is 128 elements
+    # (kv_rank + rot_dim), retention heads of 128 x 128, experts in groups
+    "2048": dict(NUFUPEL_SIZES["2048"], lat_heads=16, lat_dim=64, rot_dim=64, lat_v=64, q_rank=512, kv_rank=64,
+                 ret_heads=16, ret_dim=128, ret_v=128, groups=4, keep=2),
+    "4096": dict(NUFUPEL_SIZES["4096"], lat_heads=16, lat_dim=128, rot_dim=64, lat_v=128, q_rank=768, kv_rank=64,
+                 ret_heads=32, ret_dim=128, ret_v=128, groups=8, keep=4),
+}
+
+
+def nikonex_config(z: dict) -> dict:
+    lat = {"heads": z["lat_heads"], "dim": z["lat_dim"], "rot_dim": z["rot_dim"], "vdim": z["lat_v"], "q_rank": z["q_rank"],
+           "kv_rank": z["kv_rank"], "scale": (z["lat_dim"] + z["rot_dim"]) ** -0.5, "mask": {"size": z["window"]},
+           "rot": {"dims": z["rot_dim"], "base": 500000.0,
+                   "scaling": {"factor": 8.0, "original": 2048, "fast": 32.0, "slow": 1.0}}}
+    ret = {"heads": z["ret_heads"], "dim": z["ret_dim"], "vdim": z["ret_v"],
+           "decay": [1.0 - 2.0 ** (-5.0 - 6.0 * i / max(z["ret_heads"] - 1, 1)) for i in range(z["ret_heads"])],
+           "rot": {"dims": z["ret_dim"], "base": 500000.0}}
+    moe = {"kind": "moe", "expert": {"ff": z["eff"]}, "shared": {"ff": z["shared"]},
+           "router": {"experts": z["experts"], "top": z["top"], "scale": 2.5, "groups": {"count": z["groups"], "keep": z["keep"]}}}
+    layers = [{"type": "retention" if i % 2 == 0 else "latent_attention", "mixer": ret if i % 2 == 0 else lat, "mlp": moe}
+              for i in range(z["layers"])]
+    return {"architecture": "Nikonex", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6}, "residual_mult": 0.6,
+            "layers": layers}
+
+
+def nikonex_kernels(z: dict, T: int, peaks: dict) -> dict:
+    """Every kernel that the design adds (or runs with options of its own), alone at this size for T token rows (one
+    prompt of T tokens, or T sequences of one token after 512), beside the like kernel of the closest existing path:
+    microseconds, and algorithmic bytes (or FLOPs) over the time as a fraction of the measured peaks."""
+    import torch
+    from odin_infer_b200.csrc import ops
+    from odin_infer_b200.engine import runtime as R
+    dev, bf = "cuda:0", torch.bfloat16
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    d, E, top, eff = z["width"], z["experts"], z["top"], z["eff"]
+    H, e, r, ev, qr, kvr = z["lat_heads"], z["lat_dim"], z["rot_dim"], z["lat_v"], z["q_rank"], z["kv_rank"]
+    L = kvr + r
+    always = z["shared"] // eff
+    decode = T <= 64
+    out = {}
+
+    def replayed(fn, flush, reps=5, inner=20):
+        fn()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for _ in range(inner):
+                fn()
+        return _timed(graph.replay, flush, reps) / inner
+    timed = replayed if decode else _timed
+
+    def note(name, us, nbytes=None, flops=None, **more):
+        rec = {"us": round(us, 2)}
+        if nbytes is not None:
+            rec["of_hbm"] = round(nbytes / (us * 1e-6) / 1e9 / peaks["hbm_gbs"], 3)
+        if flops is not None:
+            rec["tflops"] = round(flops / (us * 1e-6) / 1e12, 2)
+            rec["of_bf16"] = round(flops / (us * 1e-6) / 1e12 / peaks["bf16_tflops"], 3)
+        rec.update(more)
+        out[name] = rec
+    rt = R.Runtime(dev, bf)
+    torch.manual_seed(0)
+    h = torch.randn(T, d, device=dev).to(bf)
+    x = torch.randn(T, d, device=dev)
+    w1 = torch.randn(d, device=dev).to(bf)
+    hb = torch.empty(T, d, dtype=bf, device=dev)
+    # norms: two updates with and without the factor; the second norm of the same x
+    d1, d2 = torch.randn(T, d, device=dev), torch.randn(T, d, device=dev)
+    nb = T * d * (4 * 4 + 2)
+    note("add + RMSNorm of two updates (nufupel)", timed(lambda: ops.row_update(x, [d1, d2], None, w1, 1e-6, 1, hb), flush), nbytes=nb)
+    note("add + RMSNorm of two updates times a factor", timed(lambda: ops.row_update(x, [d1, d2], None, w1, 1e-6, 1, hb, scale=0.6), flush), nbytes=nb)
+    note("the second norm of the same x", timed(lambda: ops.row_update(x, None, None, w1, 1e-6, 1, hb), flush), nbytes=T * d * 6)
+    # sequences and pages: one prompt of T tokens, or T sequences of one token after 512
+    ctx = 512 if decode else 0
+    n_seq = T if decode else 1
+    per_seq = (ctx + 1 + 63) // 64 if decode else (T + 63) // 64
+    n_pages = n_seq * per_seq
+    bt = torch.arange(n_pages, dtype=torch.int32, device=dev).reshape(n_seq, per_seq).contiguous()
+    pos = torch.full((T,), ctx, dtype=torch.int32, device=dev) if decode else torch.arange(T, dtype=torch.int32, device=dev)
+    seq = torch.arange(T, dtype=torch.int32, device=dev) if decode else torch.zeros(T, dtype=torch.int32, device=dev)
+    starts = torch.arange(0, T + 1, 1 if decode else T, dtype=torch.int32, device=dev)
+    slots = torch.arange(n_seq, dtype=torch.int32, device=dev)
+    # preparation of rows: the latent one beside the heads' one
+    Hq, Hkv, hd = z["heads"], z["kv"], z["hd"]
+    down = torch.randn(T, qr + L, device=dev).to(bf)
+    cq = torch.empty(T, qr, dtype=bf, device=dev)
+    qn, cn = torch.ones(qr, dtype=bf, device=dev), torch.ones(kvr, dtype=bf, device=dev)
+    cos, sin = torch.randn(max(T, ctx + 1), r // 2, device=dev), torch.randn(max(T, ctx + 1), r // 2, device=dev)
+    rows = (torch.randn(n_pages, 1, 64, L, device=dev) * 0.3).to(bf)
+    note("latent preparation (two norms, rotation, cache row)",
+         timed(lambda: ops.latent_prep(down, qr, kvr, r, True, qn, cn, 1e-6, cq, cos, sin, pos, seq, bt, rows), flush), nbytes=T * (qr + L) * 4)
+    kc = (torch.randn(n_pages, Hkv, 64, hd, device=dev) * 0.3).to(bf)
+    vc = (torch.randn(n_pages, Hkv, 64, hd, device=dev) * 0.3).to(bf)
+    qkv = torch.randn(T, (Hq + 2 * Hkv) * hd, device=dev).to(bf)
+    hn = torch.ones(hd, dtype=bf, device=dev)
+    ch = torch.randn(max(T, ctx + 1), hd // 2, device=dev)
+    q_out = torch.empty(T, Hq * hd, dtype=bf, device=dev)
+    note("head preparation (nufupel)", timed(lambda: ops.head_prep(qkv, Hq, Hkv, hd, hn, hn, 1e-6, ch, ch, hd, pos, seq, bt, kc, vc, q_out=q_out), flush),
+         nbytes=T * (Hq + 2 * Hkv) * hd * 4)
+    # the products per head around attention, and the queries' rotation into the wide row
+    q = (torch.randn(T, H * (e + r), device=dev) * 0.3).to(bf)
+    w_uk = (torch.randn(H, e, kvr, device=dev) / e ** 0.5).to(bf)
+    w_uv = (torch.randn(H, kvr, ev, device=dev) / kvr ** 0.5).to(bf)
+    qf = torch.empty(T, H * L, dtype=bf, device=dev)
+    note("queries onto the latent, a product per head", timed(lambda: ops.heads_linear(q, e + r, w_uk, qf, L), flush),
+         flops=2.0 * T * H * e * kvr, nbytes=T * H * (e + kvr) * 2 + w_uk.numel() * 2)
+    note("queries' rotated part into the wide row", timed(lambda: ops.rope_heads(q[:, e:], e + r, qf[:, kvr:], L, H, r, r, True, cos, sin, pos), flush),
+         nbytes=T * H * r * 4)
+    o = torch.empty(T, H * L, dtype=bf, device=dev)
+    ov = torch.empty(T, H * ev, dtype=bf, device=dev)
+    note("values from the latent, a product per head", timed(lambda: ops.heads_linear(o, L, w_uv, ov, ev), flush),
+         flops=2.0 * T * H * kvr * ev, nbytes=T * H * (kvr + ev) * 2 + w_uv.numel() * 2)
+    # attention: every head over one shared row of L elements, beside grouped-query attention
+    win = z["window"]
+    if decode:
+        for name, qq, oo, nq, nkv, dim, k_, v_ in (("decode attention over 512 keys (nufupel)", q_out, torch.empty_like(q_out), Hq, Hkv, hd, kc, vc),
+                                                    ("decode attention over 512 shared rows", qf, o, H, 1, L, rows, rows)):
+            n_split = R.decode_key_splits(T, nkv, ctx + 1)
+            scratch = torch.empty(ops.attention_decode_scratch(T, nq, dim, n_split), dtype=torch.float32, device=dev)
+            nbytes = T * (ctx + 1) * nkv * dim * 2 * (2 if k_ is not v_ else 1)
+            note(name, timed(lambda: ops.attention_decode(qq, oo, nq, nkv, dim, k_, v_, pos, seq, bt, win, scratch, n_split, 0, dim ** -0.5, 0.0), flush), nbytes=nbytes)
+    else:
+        lens = torch.tensor([T], dtype=torch.int32, device=dev)
+        pairs_seen = win * (win + 1) // 2 + (T - win) * win if T > win else T * (T + 1) // 2
+        note("prompt attention in the window (nufupel)",
+             timed(lambda: ops.attention_prefill(q_out, torch.empty_like(q_out), 1, T, Hq, Hkv, hd, kc, vc, starts, lens, bt, win, 0, hd ** -0.5, 0.0), flush),
+             flops=4.0 * Hq * hd * pairs_seen)
+        note("prompt attention in the window over shared rows",
+             timed(lambda: ops.attention_prefill(qf, o, 1, T, H, 1, L, rows, rows, starts, lens, bt, win, 0, L ** -0.5, 0.0), flush),
+             flops=4.0 * H * L * pairs_seen)
+    # retention's recurrence beside the gated recurrence (Tovalix) at equal heads and sizes
+    RH, dk, dv = z["ret_heads"], z["ret_dim"], z["ret_v"]
+    n_state = RH * dk * dv
+    state = torch.zeros(n_seq, n_state, device=dev)
+    qkvg = torch.randn(T, RH * (2 * dk + 2 * dv), device=dev)
+    rq, rk, rv, rg = qkvg[:, :RH * dk], qkvg[:, RH * dk:2 * RH * dk], qkvg[:, 2 * RH * dk:2 * RH * dk + RH * dv], qkvg[:, 2 * RH * dk + RH * dv:]
+    ro = torch.empty(T, RH * dv, device=dev)
+    decay = torch.full((RH * dk,), 0.99, device=dev)
+    c0, c1 = torch.randn(RH * dk, device=dev) - 2, torch.rand(RH * dk, device=dev)
+    cr, sr = torch.randn(max(T, ctx + 1), dk // 2, device=dev), torch.randn(max(T, ctx + 1), dk // 2, device=dev)
+    both = qkvg[:, :2 * RH * dk]
+    note("rotation of q and k in place, k scaled", timed(lambda: ops.rope_heads(both, dk, both, dk, 2 * RH, dk, dk, False, cr, sr, pos, scale=dk ** -0.5, scale_from_head=RH), flush),
+         nbytes=T * 2 * RH * dk * 8)
+    qkvg.normal_()
+    blocks = dict(block_len=128, max_new=T) if not decode else {}
+    nbytes = 4 * (T * RH * (2 * dk + 2 * dv) + 2 * n_seq * n_state)
+    if not decode:
+        nbytes += 4 * (2 * T * RH * dk + 3 * (T // 128) * n_state)
+    tag = " in blocks of 128 tokens" if not decode else ""
+    note(f"recurrence with a forget gate ({RH} heads of {dk} x {dv}; tovalix)" + tag,
+         timed(lambda: ops.linear_recurrence("gated", rq, None, rk, rv, c0, c1, ro, state, starts, slots, n_seq, RH, dk, dv, **blocks), flush),
+         nbytes=nbytes - 4 * T * RH * dk)
+    note(f"recurrence with a fixed decay ({RH} heads of {dk} x {dv})" + tag,
+         timed(lambda: ops.linear_recurrence("fixed", rq, rk, None, rv, decay, decay, ro, state, starts, slots, n_seq, RH, dk, dv, **blocks), flush),
+         nbytes=nbytes)
+    y = torch.empty(T, RH * dv, dtype=bf, device=dev)
+    wn = torch.ones(dv, dtype=bf, device=dev)
+    note("heads' norm with a weight (tovalix)", timed(lambda: ops.head_unit_scale(ro, wn, False, None, 1e-5, y, RH, dv), flush), nbytes=T * RH * dv * 6)
+    note("heads' unit norm times silu(gate)", timed(lambda: ops.head_unit_scale(ro, None, False, rg, 1e-5, y, RH, dv), flush), nbytes=T * RH * dv * 10)
+    # router: softmax over the chosen beside sigmoid scores in groups with the shared expert's gate as one more row
+    wr = (torch.randn(E + 1, d, device=dev) / d ** 0.5).to(bf)
+    ids = torch.empty(T, top + always, dtype=torch.int32, device=dev)
+    wts = torch.empty(T, top + always, dtype=torch.float32, device=dev)
+
+    def route(score, **kw):
+        w = wr if kw.get("gate_row") else wr[:E]
+        lg = rt.linear(h, w, out_dtype=torch.float32) if T > 64 else None
+        ops.moe_router(h, w, None, top, always, seq, ids, wts, lg, score=score, **kw)
+    rb = T * d * 2 + E * d * 2
+    note("router, softmax of the chosen (nufupel)", timed(lambda: route("softmax_of_chosen"), flush), nbytes=rb)
+    note("router, sigmoid scores in groups, the shared expert's gate",
+         timed(lambda: route("sigmoid_in_groups", groups=z["groups"], keep=z["keep"], route_scale=2.5, gate_row=True), flush), nbytes=rb)
+    # experts: relu^2 without a gate matrix beside silu with one
+    n_e = E + always
+    used = len(torch.unique(ids))
+    wg = (torch.randn(n_e, 2 * eff, d, device=dev) * 0.02).to(bf)
+    wd = (torch.randn(n_e, d, eff, device=dev) * 0.02).to(bf)
+    note("experts with a gate matrix, silu (nufupel; all their launches)", timed(lambda: rt.experts(h, wg, wd, ids, wts, "silu"), flush),
+         flops=2.0 * T * (top + always) * 3 * eff * d, nbytes=used * 3 * eff * d * 2, experts_used=used)
+    wu = wg[:, :eff].contiguous()
+    note("experts without one, relu squared (all their launches)", timed(lambda: rt.experts(h, wu, wd, ids, wts, "relu2", gated=False), flush),
+         flops=2.0 * T * (top + always) * 2 * eff * d, nbytes=used * 2 * eff * d * 2, experts_used=used)
+    torch.cuda.synchronize()
+    ops.attention_prefill_check()
+    ops.attention_decode_check()
+    ops.moe_tc_check()
+    return out
+
+
+def nikonex_workload(steps: int, warmup: int) -> int:
+    """The Nikonex design at two sizes that resemble a real model's layers, beside the Nufupel design of the same
+    width, layers, vocabulary, window and experts (random weights): a prompt of 2,048 tokens in one step, decoding at
+    batch 8 after 512-token prompts (device-timed), and every kernel of the design alone beside its like."""
+    import torch
+    from odin_infer_b200 import Engine, Engine_Opts
+    from odin_infer_b200.config import config_from_dict
+    from odin_infer_b200.csrc import ops
+    peaks, peak_source = load_peaks()
+    result = {"metric": "Nikonex beside Nufupel at equal sizes: prompt of 2,048 tokens, decode at batch 8 (512-token prompts), "
+                        "bf16, random weights", "peak_source": peak_source, "sizes": {}}
+    steps = min(steps, 64)
+    for name, z in NIKONEX_SIZES.items():
+        entry = {}
+        for model, raw in (("nikonex", nikonex_config(z)), ("nufupel", nufupel_config(z))):
+            need = PROMPT + warmup + steps + 72
+            engine = Engine.random(config_from_dict(raw), WEIGHT_SEED, Engine_Opts(
+                max_ctx=CONTEXT, max_tokens=max(8 * ((need + 63) // 64 * 64), PREFILL_TOKENS + 64), max_batch=8,
+                dtype="bfloat16", verbose=False))
+            ms_pf = run_prefill(engine, z["vocab"])
+            tps, ms_step, _, launches = run_decode(engine, 8, steps, warmup, z["vocab"])
+            entry[model] = {"layers": z["layers"], "weights_gib": round(engine.weight_bytes / 2 ** 30, 2),
+                            "prefill_2048": {"ms": round(ms_pf, 3), "tokens_per_s": round(PREFILL_TOKENS / ms_pf * 1e3)},
+                            "decode_b8": {"ms_per_step": round(ms_step, 4), "tokens_per_s": round(tps, 1),
+                                          "launches_per_step": launches // steps}}
+            engine.destroy()
+            del engine
+            torch.cuda.empty_cache()
+        entry["kernels_prompt_2048_rows"] = nikonex_kernels(z, PREFILL_TOKENS, peaks)
+        entry["kernels_decode_8_rows"] = nikonex_kernels(z, 8, peaks)
+        result["sizes"][name] = entry
+    ops.gemm_tc_check()
+    print(json.dumps(result))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -689,12 +918,13 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
     ap.add_argument("--no-graphs", action="store_true", help="launch the decode step's kernels one by one (for profilers)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end run (for profilers)")
-    ap.add_argument("--workload", default="8b", choices=["8b", "1.7b-mixed", "32b-long", "tovalix", "nufupel"],
+    ap.add_argument("--workload", default="8b", choices=["8b", "1.7b-mixed", "32b-long", "tovalix", "nufupel", "nikonex"],
                     help="8b: the contract's run (default).  The others are further workloads of the baseline's list and "
                          "print a line of their own: 1.7b-mixed = Qwen3-1.7B shape, 64 prompts of 16..2048 tokens, 128 new "
                          "tokens each; 32b-long = Qwen3-32B shape, a 2,048-token prompt, decoding 1 and 8 sequences at context 8192; "
                          "tovalix = the Tovalix design beside the Qwen3 decoder at equal sizes, and its kernels alone; "
-                         "nufupel = the same for the Nufupel design")
+                         "nufupel = the same for the Nufupel design; nikonex = the Nikonex design beside Nufupel at equal sizes, "
+                         "and its kernels alone")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -710,6 +940,8 @@ def main() -> int:
         return tovalix_workload(args.steps, warmup)
     if args.workload == "nufupel":
         return nufupel_workload(args.steps, warmup)
+    if args.workload == "nikonex":
+        return nikonex_workload(args.steps, warmup)
     if args.workload != "8b":
         return other_workload(args.workload)
 

@@ -86,29 +86,39 @@ def windowed_softmax_attention(q, k, v, scale: float, window: int) -> torch.Tens
     return out
 
 
-def latent_attention(h, w, p, mx, eps, positions=None):
+def _same(t):
+    return t
+
+
+def to_bfloat16_and_back(t: torch.Tensor) -> torch.Tensor:
+    """What a tensor loses when it is stored in bfloat16: the `rnd` of the functions below, to see how far rounding
+    of activations alone moves a result (the tolerance of a comparison in bfloat16 is taken from that)."""
+    return t.to(torch.bfloat16).to(t.dtype)
+
+
+def latent_attention(h, w, p, mx, eps, positions=None, rnd=_same):
     n = h.shape[0]
     H, e, r, ev, kv_rank = mx["heads"], mx["dim"], mx["rot_dim"], mx["vdim"], mx["kv_rank"]
     positions = list(range(n)) if positions is None else positions
-    cq = rms(h @ w[p + "dq"].T, w[p + "dq.norm"], eps)
-    q = (cq @ w[p + "uq"].T).view(n, H, e + r)
+    cq = rnd(rms(h @ w[p + "dq"].T, w[p + "dq.norm"], eps))
+    q = rnd(cq @ w[p + "uq"].T).view(n, H, e + r)
     down = h @ w[p + "dkv"].T
-    c = rms(down[:, :kv_rank], w[p + "dkv.norm"], eps)
+    c = rnd(rms(down[:, :kv_rank], w[p + "dkv.norm"], eps))
     k_rot = down[:, kv_rank:].view(n, 1, r)
     rot = mx["rot"]
     freqs, gain = ramp_frequencies(rot["dims"], rot["base"], rot.get("scaling"))
     q_rot = rotate(q[:, :, e:], positions, freqs, gain, "pairs")
-    k_rot = rotate(k_rot, positions, freqs, gain, "pairs")
+    k_rot = rnd(rotate(k_rot, positions, freqs, gain, "pairs"))
     k_flat = (c @ w[p + "uk"].T).view(n, H, e)
     v = (c @ w[p + "uv"].T).view(n, H, ev)
     qq = torch.cat([q[:, :, :e], q_rot], dim=2)
     kk = torch.cat([k_flat, k_rot.expand(n, H, r)], dim=2)
     window = (mx.get("mask") or {}).get("size", 0)
     o = windowed_softmax_attention(qq, kk, v, float(mx["scale"]), window)
-    return o.reshape(n, H * ev) @ w[p + "o"].T
+    return rnd(o.reshape(n, H * ev)) @ w[p + "o"].T
 
 
-def retention(h, w, p, mx, eps, positions=None, state=None):
+def retention(h, w, p, mx, eps, positions=None, state=None, rnd=_same):
     """state: None (a sequence from its start) or a list of H [e, ev] matrices that is updated in place."""
     n = h.shape[0]
     H, e, ev = mx["heads"], mx["dim"], mx["vdim"]
@@ -133,11 +143,11 @@ def retention(h, w, p, mx, eps, positions=None, state=None):
     o = rms(o, None, eps)
     g = h @ w[p + "g"].T
     y = o.reshape(n, H * ev) * (g * torch.sigmoid(g))
-    return y @ w[p + "o"].T
+    return rnd(y) @ w[p + "o"].T
 
 
-def relu2_mlp(h, up, down):
-    return torch.relu(h @ up.T) ** 2 @ down.T
+def relu2_mlp(h, up, down, rnd=_same):
+    return rnd(torch.relu(h @ up.T) ** 2) @ down.T
 
 
 def route(h, w_router, router: dict):
@@ -161,36 +171,37 @@ def route(h, w_router, router: dict):
     return ids, torch.stack(wts)
 
 
-def expert_mlp(h, w, p, mlp):
+def expert_mlp(h, w, p, mlp, rnd=_same):
     ids, wts = route(h, w[p + "router"], mlp["router"])
     out = torch.zeros(h.shape[0], h.shape[1], dtype=F64)
     for t in range(h.shape[0]):
         for k, e in enumerate(ids[t]):
-            out[t] += wts[t, k] * relu2_mlp(h[t:t + 1], w[f"{p}e{e}.up"], w[f"{p}e{e}.down"])[0]
+            out[t] += wts[t, k] * relu2_mlp(h[t:t + 1], w[f"{p}e{e}.up"], w[f"{p}e{e}.down"], rnd)[0]
     if mlp.get("shared") is not None:
         gate = torch.sigmoid(h @ w[p + "shared.sg"].T)      # [n, 1]
-        out = out + gate * relu2_mlp(h, w[p + "shared.up"], w[p + "shared.down"])
+        out = out + gate * relu2_mlp(h, w[p + "shared.up"], w[p + "shared.down"], rnd)
     return out
 
 
-def forward(config: dict, weights: dict, tokens, return_layers: bool = False):
-    """Logits [n, vocab] of a whole sequence (and the residual stream after every layer)."""
+def forward(config: dict, weights: dict, tokens, return_layers: bool = False, rnd=_same):
+    """Logits [n, vocab] of a whole sequence (and the residual stream after every layer).  rnd: applied to what a
+    16-bit engine would store in 16 bits (what a matrix product reads, cached rows); the identity by default."""
     w = {k: (v.to(F64) if v.is_floating_point() else v) for k, v in weights.items()}
     eps, m = float(config["norm"]["eps"]), float(config.get("residual_mult", 1.0))
     x = w["embed"][torch.as_tensor(tokens, dtype=torch.long)]
     streams = []
     for i, layer in enumerate(config["layers"]):
         p = f"l{i}."
-        h1 = rms(x, w[p + "norm1"], eps)
+        h1 = rnd(rms(x, w[p + "norm1"], eps))
         if layer["type"] == "latent_attention":
-            upd = latent_attention(h1, w, p + "mix.", layer["mixer"], eps)
+            upd = latent_attention(h1, w, p + "mix.", layer["mixer"], eps, rnd=rnd)
         elif layer["type"] == "retention":
-            upd = retention(h1, w, p + "mix.", layer["mixer"], eps)
+            upd = retention(h1, w, p + "mix.", layer["mixer"], eps, rnd=rnd)
         else:
             raise ValueError(f"layer {i}: unknown type {layer['type']!r}")
         if layer.get("mlp") is not None:
-            upd = upd + expert_mlp(rms(x, w[p + "norm2"], eps), w, p + "mlp.", layer["mlp"])
+            upd = upd + expert_mlp(rnd(rms(x, w[p + "norm2"], eps)), w, p + "mlp.", layer["mlp"], rnd)
         x = x + m * upd
         streams.append(x.clone())
-    logits = rms(x, w["final.norm"], eps) @ w["head"].T
+    logits = rnd(rms(x, w["final.norm"], eps)) @ w["head"].T
     return (logits, torch.stack(streams)) if return_layers else logits
