@@ -29,6 +29,7 @@ constexpr int UMMA_K = 16;
 
 #define MOE_ACT_SILU 1
 #define MOE_ACT_GELU_TANH 2
+#define MOE_ACT_RELU2 4
 
 // ------------------------------------------------------------------------------------------------ plan
 // One CTA.  ids: [rows] expert of every row (-1: none).  Outputs: place_of_row [rows] (-1: none), row_of_place
@@ -171,6 +172,12 @@ __device__ __forceinline__ float act_gate(int act, float g) {
     return __fdividef(g, 1.0f + __expf(-y2));
 }
 
+// an expert without a gate matrix: the activation of its one accumulator (relu2: max(z, 0)^2)
+__device__ __forceinline__ float act_alone(int act, float z) {
+    if (act == MOE_ACT_RELU2) { const float r = fmaxf(z, 0.f); return r * r; }
+    return act_gate(act, z);
+}
+
 template <bool DUAL, typename TO>
 __global__ void __launch_bounds__(192)
 moe_grouped_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, const GroupedParams p) {
@@ -272,6 +279,10 @@ moe_grouped_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                 } else {
                     tc::tmem_ld32(taddr, r);
                     tc::tmem_ld_wait();
+                    if (p.act != 0) {
+#pragma unroll
+                        for (int q = 0; q < 32; ++q) r[q] = __float_as_uint(act_alone(p.act, __uint_as_float(r[q])));
+                    }
                 }
                 const int j0 = tile_n * TILE_N + c0;
                 if (j0 < p.N) {
@@ -429,7 +440,7 @@ extern "C" int odin_moe_combine(const float* c, const int* place_of_row, const f
 
 // a: [places, K] bfloat16 sorted rows; w: [experts * rows_per_expert, K] bfloat16, the experts' matrices stacked.
 // dual = 1: rows_per_expert = 2 N (N gate rows, then N up rows), out[places, N] = act(a Wg^T) * (a Wu^T), bfloat16;
-// dual = 0: rows_per_expert = N, out[places, N] = a W^T in 32-bit.
+// dual = 0: rows_per_expert = N, out[places, N] = a W^T in 32-bit (act = 0), or act(a W^T) in bfloat16 (silu, gelu_tanh, relu2).
 extern "C" int odin_moe_grouped(const void* a, long long lda, const void* w, long long ldw, int n_experts, int rows_per_expert,
                                 int places, int N, int K, int dual, int act, const int* tile_expert, void* out, long long ldc,
                                 void* stream) {
@@ -447,6 +458,10 @@ extern "C" int odin_moe_grouped(const void* a, long long lda, const void* w, lon
     p.error = error_flag();
     cudaStream_t s = (cudaStream_t)stream;
     if (dual) return launch_grouped<true, bf16>(ma, mw, p, places / BM, s);
+    if (act != 0) {
+        if (act != MOE_ACT_SILU && act != MOE_ACT_GELU_TANH && act != MOE_ACT_RELU2) return ODIN_ERR_BAD_ARG;
+        return launch_grouped<false, bf16>(ma, mw, p, places / BM, s);
+    }
     return launch_grouped<false, float>(ma, mw, p, places / BM, s);
 }
 

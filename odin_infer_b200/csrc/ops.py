@@ -151,13 +151,15 @@ def _parts(t: torch.Tensor, rows: int, cols: int) -> tuple[int, int]:
 
 def row_update(x: torch.Tensor, delta, bias: torch.Tensor | None, weight: torch.Tensor | None,
                eps: float, groups: int, out: torch.Tensor | None, rows: torch.Tensor | None = None,
-               normalise: bool = True, scale: float = 1.0) -> None:
+               normalise: bool = True, scale: float = 1.0, weight2: torch.Tensor | None = None,
+               out2: torch.Tensor | None = None) -> None:
     """x += sum of delta's parts + bias (in place, 32-bit; not with a row gather), then
     normalise: out = weight * x / rms, the root mean square taken over each of `groups` equal
     consecutive parts of the row by itself (out may be x: in place); else out = x converted
     (out None: the update alone).  delta may be a list of up to three updates (each [n, d] or
     [parts, n, d]; all but the first 32-bit), which are added in their order.  scale != 1: the updates (and the
-    bias) are added up by themselves and x += scale * their sum."""
+    bias) are added up by themselves and x += scale * their sum.  out2 with weight2: a second norm of the same row,
+    out2 = weight2 * x / rms with the root mean square formed once (out's dtype and shape)."""
     d = x.shape[-1]
     assert x.dtype == torch.float32 and x.is_contiguous()
     more = []
@@ -166,8 +168,12 @@ def row_update(x: torch.Tensor, delta, bias: torch.Tensor | None, weight: torch.
     n_split, stride = (1, 0)
     if delta is not None:
         n_split, stride = _parts(delta, x.shape[0], d)
-    if more or (scale != 1.0 and delta is not None):
+    if more or (scale != 1.0 and delta is not None) or out2 is not None:
         assert len(more) <= 2 and all(m.dtype == torch.float32 for m in more)
+        if out2 is not None:
+            assert normalise and weight2 is not None and weight2.numel() == d and out is not None
+            assert out2.is_contiguous() and out2.shape == out.shape and out2.dtype == out.dtype
+            assert out2.data_ptr() not in (x.data_ptr(), out.data_ptr())
         extra = []
         for m in more + [None] * (2 - len(more)):
             ns, st = _parts(m, x.shape[0], d) if m is not None else (0, 0)
@@ -180,11 +186,13 @@ def row_update(x: torch.Tensor, delta, bias: torch.Tensor | None, weight: torch.
         if normalise:
             assert weight is not None and weight.numel() == d and out is not None and d % groups == 0
         _check(_fn("rowwise", "odin_row_update_several")(
-            _ptr(x), _ptr(delta), c_int(dtype_code(delta.dtype)), c_int(n_split), c_longlong(stride), *extra,
+            _ptr(x), _ptr(delta), c_int(dtype_code(delta.dtype) if delta is not None else 0), c_int(n_split),
+            c_longlong(stride), *extra,
             _ptr(bias), c_int(dtype_code(bias.dtype) if bias is not None else 0), _ptr(weight),
             c_int(dtype_code(weight.dtype) if weight is not None else 0), c_float(eps), c_int(groups),
             c_int(0 if normalise else 1), _ptr(out), c_int(dtype_code(out.dtype) if out is not None else 0), _ptr(rows),
-            c_int(n_rows), c_int(d), c_float(scale), _stream()), "row_update")
+            c_int(n_rows), c_int(d), c_float(scale), _ptr(weight2),
+            c_int(dtype_code(weight2.dtype) if weight2 is not None else 0), _ptr(out2), _stream()), "row_update")
         return
     if out is not None:
         assert out.is_contiguous() and out.shape[-1] == d
@@ -365,14 +373,25 @@ def moe_gather(h: torch.Tensor, row_of_place: torch.Tensor, per: int, out: torch
                                             c_int(per), c_int(h.shape[1]), _ptr(out), _stream()), "moe_gather")
 
 
-def moe_grouped(a: torch.Tensor, w: torch.Tensor, tile_expert: torch.Tensor, out: torch.Tensor, kind: str | None = None) -> None:
+def moe_grouped(a: torch.Tensor, w: torch.Tensor, tile_expert: torch.Tensor, out: torch.Tensor, kind: str | None = None,
+                gated: bool = True) -> None:
     """Every tile of 128 sorted rows of a [places, K] times the matrix of the tile's own expert (tcgen05).
     kind None: w [experts, N, K], out float32 [places, N] = a W[e]^T.  kind silu / gelu_tanh: w [experts, 2 N, K]
-    (gate rows first), out bfloat16 [places, N] = act(a Wg[e]^T) * (a Wu[e]^T)."""
+    (gate rows first), out bfloat16 [places, N] = act(a Wg[e]^T) * (a Wu[e]^T).  kind with gated=False (also relu2):
+    w [experts, N, K], out bfloat16 [places, N] = act(a W[e]^T), the activation applied as the sums are read back."""
     places, K = a.shape
     n_e, rpe = w.shape[0], w.shape[1]
     N = out.shape[1]
-    dual = kind is not None
+    dual = kind is not None and gated
+    if kind is not None and not gated:
+        assert a.dtype == w.dtype == torch.bfloat16 and a.is_contiguous() and w.is_contiguous() and w.shape[2] == K
+        assert out.is_contiguous() and out.shape[0] == places and out.dtype == torch.bfloat16
+        assert tile_expert.numel() * 128 == places and rpe == N
+        _check(_fn("moe_tc", "odin_moe_grouped")(
+            _ptr(a), c_longlong(a.stride(0)), _ptr(w), c_longlong(K), c_int(n_e), c_int(rpe), c_int(places), c_int(N), c_int(K),
+            c_int(0), c_int(ACTIVATIONS[kind]), _ptr(tile_expert), _ptr(out), c_longlong(out.stride(0)), _stream()),
+            "moe_grouped")
+        return
     assert a.dtype == w.dtype == torch.bfloat16 and a.is_contiguous() and w.is_contiguous() and w.shape[2] == K
     assert out.is_contiguous() and out.shape[0] == places and out.dtype == (torch.bfloat16 if dual else torch.float32)
     assert tile_expert.numel() * 128 == places and rpe == (2 * N if dual else N)

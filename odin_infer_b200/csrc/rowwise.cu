@@ -22,11 +22,15 @@
 // pointer is 16-byte aligned, so everything moves four elements at a time; the same sums in the same order.
 // more: up to two further updates (32-bit, each with parts of its own), added after `delta` in their order.
 // scale != 1: the updates and the bias are added up by themselves first, and x_new = x + scale * their sum.
+// out2 (mode 0): a second norm of the same x_new with a weight of its own, out2 = w2 * (x_new / rms), the root mean
+// square formed once (a block whose two sublayers each read their own norm of one residual stream).
 struct MoreDeltas {
     const float* p[2];
     int n_split[2];
     long long stride[2];
     float scale;
+    VecRef w2;
+    void* out2;
 };
 
 template <typename TD, typename TO, bool VEC>
@@ -41,9 +45,12 @@ row_update_kernel(float* x, const TD* __restrict__ delta, int n_split, size_t sp
     if (rows != nullptr) src = rows[r];
     pdl_wait();
     TO* o = out == nullptr ? nullptr : out + (size_t)r * d;
+    TO* o2 = (mode == 0 && more.out2 != nullptr) ? reinterpret_cast<TO*>(more.out2) + (size_t)r * d : nullptr;
     if (src < 0) {
         if (o != nullptr && (void*)out != (void*)x)
             for (int j = threadIdx.x; j < d; j += blockDim.x) o[j] = from_f32<TO>(0.f);
+        if (o2 != nullptr)
+            for (int j = threadIdx.x; j < d; j += blockDim.x) o2[j] = from_f32<TO>(0.f);
         return;
     }
     float* xr = x + (size_t)src * d;
@@ -132,6 +139,10 @@ row_update_kernel(float* x, const TD* __restrict__ delta, int n_split, size_t sp
                 const float4 v = ld4(rowbuf + c), wv = w.at4(c);
                 if (keep) st4(xr + c, v);
                 st4(o + c, make_float4(wv.x * (rs * v.x), wv.y * (rs * v.y), wv.z * (rs * v.z), wv.w * (rs * v.w)));
+                if (o2 != nullptr) {
+                    const float4 w2 = more.w2.at4(c);
+                    st4(o2 + c, make_float4(w2.x * (rs * v.x), w2.y * (rs * v.y), w2.z * (rs * v.z), w2.w * (rs * v.w)));
+                }
             }
         } else {
             for (int j = threadIdx.x; j < gsz; j += blockDim.x) {
@@ -139,6 +150,7 @@ row_update_kernel(float* x, const TD* __restrict__ delta, int n_split, size_t sp
                 const float v = rowbuf[c];
                 if (keep) xr[c] = v;
                 o[c] = from_f32<TO>(w.at(c) * (rs * v));
+                if (o2 != nullptr) o2[c] = from_f32<TO>(more.w2.at(c) * (rs * v));
             }
         }
     }
@@ -159,7 +171,7 @@ static int row_update_launch(float* x, const void* delta, int delta_dtype, int n
     const bool vec = (d % 4 == 0) && (gsz % 4 == 0) && (split_stride % 4 == 0) && (more.stride[0] % 4 == 0) &&
                      (more.stride[1] % 4 == 0) &&
                      ((((uintptr_t)x) | ((uintptr_t)delta) | ((uintptr_t)bias) | ((uintptr_t)w) | ((uintptr_t)out) |
-                       ((uintptr_t)more.p[0]) | ((uintptr_t)more.p[1])) % 16 == 0);
+                       ((uintptr_t)more.p[0]) | ((uintptr_t)more.p[1]) | ((uintptr_t)more.w2.p) | ((uintptr_t)more.out2)) % 16 == 0);
 #define GO(TD, TO)                                                                                               \
     do {                                                                                                         \
         auto kern = vec ? row_update_kernel<TD, TO, true> : row_update_kernel<TD, TO, false>;                    \
@@ -182,19 +194,23 @@ static int row_update_launch(float* x, const void* delta, int delta_dtype, int n
 extern "C" int odin_row_update(float* x, const void* delta, int delta_dtype, int n_split, long long split_stride,
                                const void* bias, int bias_dtype, const void* w, int w_dtype, float eps, int groups,
                                int mode, void* out, int out_dtype, const int* rows, int n_rows, int d, void* stream) {
-    MoreDeltas more{{nullptr, nullptr}, {0, 0}, {0, 0}, 1.0f};
+    MoreDeltas more{{nullptr, nullptr}, {0, 0}, {0, 0}, 1.0f, VecRef{nullptr, false}, nullptr};
     return row_update_launch(x, delta, delta_dtype, n_split, split_stride, bias, bias_dtype, w, w_dtype, eps, groups, mode,
                              out, out_dtype, rows, n_rows, d, more, stream);
 }
 
 // The same with up to two further 32-bit updates (null: none), each [parts][n, d], added after `delta`, and a factor
-// on the sum of all updates (x_new = x + scale * (updates + bias)).
+// on the sum of all updates (x_new = x + scale * (updates + bias)); and with a second normalised output out2 = w2 * x_new / rms
+// (null: none; of out's type, never x itself, with a root mean square over the same groups).
 extern "C" int odin_row_update_several(float* x, const void* delta, int delta_dtype, int n_split, long long split_stride,
                                        const float* delta2, int n_split2, long long split_stride2, const float* delta3,
                                        int n_split3, long long split_stride3, const void* bias, int bias_dtype,
                                        const void* w, int w_dtype, float eps, int groups, int mode, void* out,
-                                       int out_dtype, const int* rows, int n_rows, int d, float scale, void* stream) {
-    MoreDeltas more{{delta2, delta3}, {n_split2, n_split3}, {split_stride2, split_stride3}, scale};
+                                       int out_dtype, const int* rows, int n_rows, int d, float scale, const void* w2,
+                                       int w2_dtype, void* out2, void* stream) {
+    if (out2 != nullptr && (mode != 0 || w2 == nullptr || out2 == (void*)x || out2 == out)) return ODIN_ERR_BAD_ARG;
+    MoreDeltas more{{delta2, delta3}, {n_split2, n_split3}, {split_stride2, split_stride3}, scale,
+                    VecRef{w2, w2_dtype == ODIN_BF16}, out2};
     return row_update_launch(x, delta, delta_dtype, n_split, split_stride, bias, bias_dtype, w, w_dtype, eps, groups, mode,
                              out, out_dtype, rows, n_rows, d, more, stream);
 }

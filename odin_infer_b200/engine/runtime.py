@@ -245,12 +245,7 @@ class Runtime:
             hs = self.empty(places, h.shape[1])
             ops.moe_gather(h, row_of_place, per, hs)
             a = self.empty(places, inner)
-            if gated:
-                ops.moe_grouped(hs, w_gate_up, tile_expert, a, activation)
-            else:
-                u = self.empty(places, inner, dtype=torch.float32)
-                ops.moe_grouped(hs, w_gate_up, tile_expert, u)
-                ops.activation(u, activation, a)
+            ops.moe_grouped(hs, w_gate_up, tile_expert, a, activation, gated=gated)   # the activation rides in the epilogue
             c = self.empty(places, width, dtype=torch.float32)
             ops.moe_grouped(a, w_down, tile_expert, c)
             y = self.empty(T, width, dtype=torch.float32)

@@ -48,9 +48,8 @@ class PreNormBlock(Block):
         return all(p.graph_safe for p in self._parts())
 
     @staticmethod
-    def _norm(norm, rt, x, pending):
+    def _norm(norm, rt, x, pending, **more):
         delta, bias = split_update(pending)
-        more = {}
         factor = update_factor(pending)
         if factor != 1.0:
             if not norm.takes_scale:
@@ -103,9 +102,15 @@ class ParallelBlock(PreNormBlock):
     def forward(self, rt, step, x, pending, entry):
         mixer, ffn = self._mixer, self.ffn
         plain = self.residual_mult == 1.0   # else nothing may add itself to x unscaled
-        h = self._norm(self.norm_mixer, rt, x, pending)
-        # x holds everything before this block now; a second norm reads the same x
-        h2 = h if self.norm_ffn is None else self.norm_ffn.forward(rt, x, None)
+        # a second norm reads the same x, with everything before this block added: one kernel writes both where the
+        # two differ in their weights alone, else the second runs after the first has updated x
+        if self.norm_ffn is None:
+            h = h2 = self._norm(self.norm_mixer, rt, x, pending)
+        elif getattr(self.norm_mixer, "pairs_with", lambda o: False)(self.norm_ffn):
+            h, h2 = self._norm(self.norm_mixer, rt, x, pending, second=self.norm_ffn)
+        else:
+            h = self._norm(self.norm_mixer, rt, x, pending)
+            h2 = self.norm_ffn.forward(rt, x, None)
         # h is computed: a product that adds to x in its epilogue no longer changes what the sublayers read
         out = [mixer.forward(rt, step, h, entry, residual=x) if (mixer.takes_residual and plain) else mixer.forward(rt, step, h, entry)]
         if ffn is not None:

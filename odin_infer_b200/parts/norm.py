@@ -39,13 +39,25 @@ class RMSNorm(Norm):
     def kernel_groups(self):
         return {"elementwise", "rowwise"}
 
-    def forward(self, rt, x, delta, rows=None, bias=None, scale: float = 1.0):
+    def pairs_with(self, other) -> bool:
+        """Whether `other` norms the same row by the same root mean square (another weight only), so that one kernel
+        can write both outputs."""
+        return (type(other) is type(self) and other.width == self.width and other.eps == self.eps
+                and other.groups == self.groups)
+
+    def forward(self, rt, x, delta, rows=None, bias=None, scale: float = 1.0, second=None):
+        """second: a norm that `pairs_with` this one; both outputs of the one updated row come back, (out, out2)."""
         n = x.shape[0] if rows is None else rows.numel()
         out = rt.empty(n, self.width)
         if isinstance(delta, (list, tuple)) and len(delta) == 1:
             delta = delta[0]
         if delta is None and bias is None:
             scale = 1.0
+        if second is not None:
+            out2 = rt.empty(n, self.width)
+            ops.row_update(x, delta, bias, self.weight, self.eps, self.groups, out, rows, scale=scale,
+                           weight2=second.weight, out2=out2)
+            return out, out2
         if self.groups == 1 and bias is None and scale == 1.0 and not isinstance(delta, (list, tuple)):
             ops.add_rmsnorm(x, delta, self.weight, self.eps, out, rows)
         else:

@@ -706,3 +706,71 @@ def test_a_product_per_head_and_the_unit_norm_with_its_gate(dtype, tol):
     gd = g.double().cpu()
     want = P.rms(o.double().cpu().view(T, H, N), None, 1e-5).reshape(T, H * N) * gd * torch.sigmoid(gd)
     close(y, want, tol)
+
+
+@pytest.mark.parametrize("act", ["relu2", "silu", "gelu_tanh"])
+@pytest.mark.parametrize("E,K,N", [(3, 64, 40), (5, 72, 136), (2, 128, 256)])
+def test_grouped_product_without_a_gate_applies_its_activation_as_it_reads_back(act, E, K, N):
+    """Sorted rows times their tile's own expert on the tensor cores, act(a W^T) written in bfloat16: against a loop in
+    float64, over an expert without a tile, an output that is no multiple of the tile and a K that is no multiple of 64."""
+    from odin_infer_b200.csrc import ops
+    torch.manual_seed(E * K + N)
+    tiles = [0, E - 1, -1, 0] if E > 2 else [1, -1, 1]
+    tile_expert = torch.tensor(tiles, dtype=torch.int32, device=DEV)
+    places = 128 * len(tiles)
+    a = torch.randn(places, K, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(E, N, K, device=DEV) / math.sqrt(K)).to(torch.bfloat16)
+    out = torch.full((places, N), 7.0, dtype=torch.bfloat16, device=DEV)
+    ops.moe_grouped(a, w, tile_expert, out, act, gated=False)
+    torch.cuda.synchronize()
+    ops.moe_tc_check()
+    f = {"relu2": lambda z: z.clamp(min=0) ** 2, "silu": lambda z: z * torch.sigmoid(z),
+         "gelu_tanh": lambda z: 0.5 * z * (1 + torch.tanh(math.sqrt(2 / math.pi) * (z + 0.044715 * z ** 3)))}[act]
+    for i, e in enumerate(tiles):
+        rows = slice(128 * i, 128 * (i + 1))
+        if e < 0:
+            assert (out[rows] == 7.0).all()   # a tile that no expert's rows reach is left alone
+            continue
+        want = f(a[rows].double().cpu() @ w[e].double().cpu().T)
+        close(out[rows], want, 8e-3)
+
+
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("d,groups,scale,updates", [(96, 1, 0.37, 2), (130, 2, 1.0, 1), (200, 1, 1.0, 0), (64, 4, 2.5, 3)])
+def test_two_norms_of_one_updated_row(out_dtype, d, groups, scale, updates):
+    """x += scale * (sum of the updates), then two norms of that one row with weights of their own from one root mean
+    square: against float64, with and without updates, in groups, at a width that is no multiple of four, and through
+    a gather of rows (which leaves x as it was)."""
+    from odin_infer_b200.csrc import ops
+    torch.manual_seed(d + updates)
+    n = 37
+    x0 = torch.randn(n, d, device=DEV) * 3
+    first = torch.randn(n, d, device=DEV).to(out_dtype) if updates else None
+    rest = [torch.randn(2, n, d, device=DEV) if i == 0 else torch.randn(n, d, device=DEV) for i in range(max(updates - 1, 0))]
+    w1, w2 = torch.rand(d, device=DEV) + 0.5, torch.randn(d, device=DEV)
+    x = x0.clone()
+    o1, o2 = torch.empty(n, d, dtype=out_dtype, device=DEV), torch.full((n, d), 9.0, dtype=out_dtype, device=DEV)
+    delta = None if first is None else ([first] + rest if rest else first)
+    ops.row_update(x, delta, None, w1, 1e-5, groups, o1, scale=scale if updates else 1.0, weight2=w2, out2=o2)
+    torch.cuda.synchronize()
+    total = torch.zeros(n, d, dtype=torch.float64)
+    if first is not None:
+        total += first.double().cpu()
+    for m in rest:
+        total += m.double().cpu().reshape(-1, n, d).sum(0)
+    want_x = x0.double().cpu() + scale * total
+    close(x, want_x, 1e-6)
+    parts = want_x.view(n, groups, d // groups)
+    unit = (parts / torch.sqrt((parts ** 2).mean(-1, keepdim=True) + 1e-5)).reshape(n, d)
+    tol = 1e-5 if out_dtype == torch.float32 else 8e-3
+    close(o1, unit * w1.double().cpu(), tol)
+    close(o2, unit * w2.double().cpu(), tol)
+    rows = torch.tensor([5, -1, 0, 36], dtype=torch.int32, device=DEV)
+    p1, p2 = torch.empty(4, d, dtype=out_dtype, device=DEV), torch.empty(4, d, dtype=out_dtype, device=DEV)
+    kept = x.clone()
+    ops.row_update(x, None, None, w1, 1e-5, groups, p1, rows, weight2=w2, out2=p2)
+    torch.cuda.synchronize()
+    assert torch.equal(x, kept)
+    pick = torch.tensor([5, 0, 36])
+    assert torch.equal(p1[[0, 2, 3]], o1[pick.to(DEV)]) and torch.equal(p2[[0, 2, 3]], o2[pick.to(DEV)])
+    assert (p1[1] == 0).all() and (p2[1] == 0).all()
