@@ -754,6 +754,9 @@ def nikonex_kernels(z: dict, T: int, peaks: dict) -> dict:
     note("add + RMSNorm of two updates (nufupel)", timed(lambda: ops.row_update(x, [d1, d2], None, w1, 1e-6, 1, hb), flush), nbytes=nb)
     note("add + RMSNorm of two updates times a factor", timed(lambda: ops.row_update(x, [d1, d2], None, w1, 1e-6, 1, hb, scale=0.6), flush), nbytes=nb)
     note("the second norm of the same x", timed(lambda: ops.row_update(x, None, None, w1, 1e-6, 1, hb), flush), nbytes=T * d * 6)
+    w2, hb2 = torch.randn(d, device=dev).to(bf), torch.empty(T, d, dtype=bf, device=dev)
+    note("add + both norms of two updates times a factor, one kernel",
+         timed(lambda: ops.row_update(x, [d1, d2], None, w1, 1e-6, 1, hb, scale=0.6, weight2=w2, out2=hb2), flush), nbytes=nb + T * d * 2)
     # sequences and pages: one prompt of T tokens, or T sequences of one token after 512
     ctx = 512 if decode else 0
     n_seq = T if decode else 1

@@ -5,7 +5,8 @@
     python -m odin_infer_b200.csrc.microbench decode-attention --batch 64 --ctx 640
     python -m odin_infer_b200.csrc.microbench prefill-attention --tokens 2048
     python -m odin_infer_b200.csrc.microbench add-rmsnorm --rows 8 --width 4096 --split 4
-    python -m odin_infer_b200.csrc.microbench linear-recurrence --tokens 2048 --heads 32 --head-dim 64 [--gated] [--batch 8]
+    python -m odin_infer_b200.csrc.microbench linear-recurrence --tokens 2048 --heads 32 --head-dim 64 [--gated | --fixed]
+                                                                  [--batch 8] [--block-len 128]
     python -m odin_infer_b200.csrc.microbench mma-rate
 
 Prints one JSON line: the median time and the achieved bytes/s and flop/s of the kernel's
@@ -77,6 +78,9 @@ def main(argv=None) -> int:
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--gated", action="store_true", help="linear-recurrence: the gated form (default: the form with a bonus)")
     ap.add_argument("--value-dim", type=int, default=0, help="linear-recurrence: size of a value head (0: --head-dim)")
+    ap.add_argument("--fixed", action="store_true", help="linear-recurrence: a constant decay per head (retention)")
+    ap.add_argument("--block-len", type=int, default=0,
+                    help="linear-recurrence: walk blocks of this many tokens side by side (0: one walk per sequence and head)")
     args = ap.parse_args(argv)
     out: dict = {"kernel": args.kernel}
 
@@ -85,15 +89,18 @@ def main(argv=None) -> int:
         B, T1, H, dk = args.batch, args.tokens, args.heads, args.head_dim
         dv = args.value_dim or dk
         T = B * T1
-        mode = "gated" if args.gated else "bonus"
+        mode = "fixed" if args.fixed else "gated" if args.gated else "bonus"
         q, k, g = (torch.randn(T, H * dk, device=DEV) for _ in range(3))
         v, o = torch.randn(T, H * dv, device=DEV), torch.empty(T, H * dv, device=DEV)
         c0, c1 = torch.randn(H * dk, device=DEV).bfloat16() - 2, torch.rand(H * dk, device=DEV).bfloat16()
+        if mode == "fixed":
+            c0 = c1 = (1.0 - 2.0 ** (-5.0 - 6.0 * torch.arange(H, device=DEV) / max(H - 1, 1))).repeat_interleave(dk).contiguous()
         state = torch.zeros(B, H * dk * dv, device=DEV)
         starts = torch.arange(0, T + 1, T1, dtype=torch.int32, device=DEV)
         slots = torch.arange(B, dtype=torch.int32, device=DEV)
-        ms = timeit(lambda: ops.linear_recurrence(mode, q, k if mode == "bonus" else None, g, v, c0, c1, o, state, starts,
-                                                  slots, B, H, dk, dv), args.iters)
+        ms = timeit(lambda: ops.linear_recurrence(mode, q, k if mode != "gated" else None, None if mode == "fixed" else g, v,
+                                                  c0, c1, o, state, starts, slots, B, H, dk, dv,
+                                                  block_len=args.block_len, max_new=T1), args.iters)
         nbytes = 4 * (T * H * (3 * dk + 2 * dv) + 2 * B * H * dk * dv)
         out.update(form=mode, sequences=B, tokens_each=T1, heads=H, key_channels=dk, value_channels=dv, us=round(ms * 1e3, 2),
                    gbs=round(nbytes / ms / 1e6, 1), gflops=round(5 * T * H * dk * dv / ms / 1e6, 1))

@@ -125,7 +125,11 @@ linear_recurrence_kernel(RecParams p) {
     constexpr int NK = SL * REC_SPLIT;             // key channels the registers hold (dk <= NK)
     constexpr int TOK = NK > 128 ? 8 : 16;
     constexpr bool BONUS_IN_REGS = SL <= 32;
-    __shared__ __align__(16) float sq[TOK][NK], sk[TOK][NK], sw[TOK][NK];
+    // A warp's four parts read their channels at the same moment, SL floats apart: every part's channels sit four floats
+    // further on than the part before, so that the four 16-byte reads fall into different banks (SL = 32: banks 0, 4, 8, 12
+    // in place of four times bank 0).
+    constexpr int NKP = NK + 4 * REC_SPLIT;
+    __shared__ __align__(16) float sq[TOK][NKP], sk[TOK][NKP], sw[TOK][NKP];
     __shared__ float sv[TOK][REC_COLS], sb[NK];
     pdl_trigger();
     const int b = BLOCKS ? blockIdx.x / p.n_blocks : blockIdx.x, head = blockIdx.y;
@@ -205,7 +209,8 @@ linear_recurrence_kernel(RecParams p) {
                         wv = fg;
                     }
                 }
-                sq[u][i] = qv; sk[u][i] = kv; sw[u][i] = wv;
+                const int ip = i + (i / SL) * 4;
+                sq[u][ip] = qv; sk[u][ip] = kv; sw[u][ip] = wv;
             }
             if (e < nt * ccols) sv[e / ccols][e % ccols] = rv[f];
         }
@@ -223,9 +228,9 @@ linear_recurrence_kernel(RecParams p) {
             float acc0 = 0.f, acc1 = 0.f;
 #pragma unroll
             for (int i4 = 0; i4 < SL; i4 += 4) {
-                const float4 k4 = *reinterpret_cast<const float4*>(&sk[u][i0 + i4]);
-                const float4 q4 = *reinterpret_cast<const float4*>(&sq[u][i0 + i4]);
-                const float4 w4 = *reinterpret_cast<const float4*>(&sw[u][i0 + i4]);
+                const float4 k4 = *reinterpret_cast<const float4*>(&sk[u][i0 + part * 4 + i4]);
+                const float4 q4 = *reinterpret_cast<const float4*>(&sq[u][i0 + part * 4 + i4]);
+                const float4 w4 = *reinterpret_cast<const float4*>(&sw[u][i0 + part * 4 + i4]);
                 const float kk[4] = {k4.x, k4.y, k4.z, k4.w}, qq[4] = {q4.x, q4.y, q4.z, q4.w}, ww[4] = {w4.x, w4.y, w4.z, w4.w};
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
