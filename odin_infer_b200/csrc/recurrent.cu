@@ -292,25 +292,45 @@ recurrence_carry_kernel(RecParams p) {
     float* st = p.state + (size_t)slot * p.state_stride + (size_t)head * p.dk * p.dv + e;
     float S = *st;
     const int n = (row1 - row0 + p.block_len - 1) / p.block_len;
-    for (int c = 0; c < n; ++c) {
-        const size_t item = (size_t)b * p.n_blocks + c;
-        float* loc = p.s_loc + (item * p.H + head) * p.dk * p.dv + e;
-        const float own = *loc;
-        *loc = S;
-        S = fmaf(p.d_tot[item * p.H * p.dk + head * p.dk + i], S, own);
+    // eight blocks at a time: their loads go out together, then the chain of multiply-adds runs over what came back
+    constexpr int CB = 8;
+    const size_t per_item = (size_t)p.H * p.dk * p.dv, at = (size_t)head * p.dk * p.dv + e;
+    for (int c0 = 0; c0 < n; c0 += CB) {
+        const size_t item0 = (size_t)b * p.n_blocks + c0;
+        float own[CB], dec[CB];
+#pragma unroll
+        for (int u = 0; u < CB; ++u) {
+            own[u] = dec[u] = 0.f;
+            if (c0 + u < n) {
+                own[u] = p.s_loc[(item0 + u) * per_item + at];
+                dec[u] = p.d_tot[((item0 + u) * p.H + head) * p.dk + i];
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < CB; ++u)
+            if (c0 + u < n) {
+                p.s_loc[(item0 + u) * per_item + at] = S;
+                S = fmaf(dec[u], S, own[u]);
+            }
     }
     *st = S;
 }
 
-// o[t, head, :] += (q_t * decays since the block's start)^T S_in(block): eight tokens by 32 columns per CTA pass,
-// the incoming state's 32 columns in shared memory.
+// o[t, head, :] += (q_t * decays since the block's start)^T S_in(block): 64 (or 32) tokens by 32 columns per CTA pass.
+// Shared memory: the incoming state's 32 columns [dk][32], then (dk a multiple of four) 64 tokens' q [64][dk], which the
+// CTA fetches with loads that all go out together; a warp then takes eight tokens and reads four channels of a token's q
+// in one broadcast.  Every sum runs over the channels in their order, whichever path computes it.
+#define CARRY_OUT_TOK 64
 __global__ void __launch_bounds__(256)
 recurrence_carry_out_kernel(RecParams p) {
-    __shared__ float tile[REC_MAX_DK][32];
+    extern __shared__ __align__(16) float co_smem[];
+    float (*tile)[32] = reinterpret_cast<float (*)[32]>(co_smem);
+    float* qsm = co_smem + (size_t)p.dk * 32;
     pdl_trigger();
     const int item = blockIdx.x, head = blockIdx.y;
     const int b = item / p.n_blocks;
-    const int col = blockIdx.z * 32 + (threadIdx.x & 31), lane_t = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31, lane_t = threadIdx.x >> 5;
+    const int col = blockIdx.z * 32 + lane;
     const int seq_end = p.seq_start[b + 1];
     const int row0 = p.seq_start[b] + (item % p.n_blocks) * p.block_len;
     const int row1 = min(seq_end, row0 + p.block_len);
@@ -321,13 +341,51 @@ recurrence_carry_out_kernel(RecParams p) {
         const int i = e >> 5, c = blockIdx.z * 32 + (e & 31);
         tile[i][e & 31] = c < p.dv ? sin[(size_t)i * p.dv + c] : 0.f;
     }
-    __syncthreads();
     const size_t qs = (size_t)p.H * p.dk;
+    if ((p.dk & 3) == 0) {
+        const int dk4 = p.dk >> 2;
+        for (int tb = row0; tb < row1; tb += CARRY_OUT_TOK) {
+            __syncthreads();   // the pass before has read its q (and, the first time, the tile is there after the next one)
+            for (int e = threadIdx.x; e < CARRY_OUT_TOK * dk4; e += blockDim.x) {
+                const int u = e / dk4, c4 = e % dk4;
+                if (tb + u < row1)
+                    reinterpret_cast<float4*>(qsm)[e] =
+                        __ldg(reinterpret_cast<const float4*>(p.qp + (size_t)(tb + u) * qs + (size_t)head * p.dk) + c4);
+            }
+            __syncthreads();
+            const int t0 = tb + lane_t * 8;
+            const int nt = min(8, row1 - t0);
+            if (nt <= 0) continue;
+            float acc[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) acc[u] = 0.f;
+            const float* qw = qsm + (size_t)lane_t * 8 * p.dk;
+            for (int i = 0; i < p.dk; i += 4) {
+                const float s0 = tile[i][lane], s1 = tile[i + 1][lane], s2 = tile[i + 2][lane], s3 = tile[i + 3][lane];
+#pragma unroll
+                for (int u = 0; u < 8; ++u)
+                    if (u < nt) {
+                        const float4 q4 = *reinterpret_cast<const float4*>(qw + u * p.dk + i);
+                        acc[u] = fmaf(q4.x, s0, acc[u]);
+                        acc[u] = fmaf(q4.y, s1, acc[u]);
+                        acc[u] = fmaf(q4.z, s2, acc[u]);
+                        acc[u] = fmaf(q4.w, s3, acc[u]);
+                    }
+            }
+            if (col < p.dv) {
+#pragma unroll
+                for (int u = 0; u < 8; ++u)
+                    if (u < nt) p.o[(size_t)(t0 + u) * p.o_stride + (size_t)head * p.dv + col] += acc[u];
+            }
+        }
+        return;
+    }
+    __syncthreads();
     for (int t0 = row0 + lane_t * 4; t0 < row1; t0 += 32) {   // a warp takes four tokens at a time
         float acc[4] = {0.f, 0.f, 0.f, 0.f};
         const float* qrow = p.qp + (size_t)t0 * qs + (size_t)head * p.dk;
         for (int i = 0; i < p.dk; ++i) {
-            const float sv = tile[i][threadIdx.x & 31];
+            const float sv = tile[i][lane];
 #pragma unroll
             for (int u = 0; u < 4; ++u)
                 if (t0 + u < row1) acc[u] = fmaf(__ldg(qrow + u * qs + i), sv, acc[u]);
@@ -397,7 +455,12 @@ extern "C" int odin_linear_recurrence(int mode, const float* q, long long q_stri
     if (blocks) {
         odin_launch(recurrence_carry_kernel, dim3(n_seqs, H, (dk * dv + 255) / 256), dim3(256), 0, s, p);
         ODIN_LAUNCH_CHECK();
-        odin_launch(recurrence_carry_out_kernel, dim3(n_items, H, (dv + 31) / 32), dim3(256), 0, s, p);
+        const size_t co_smem = (size_t)dk * 32 * sizeof(float) + ((dk & 3) == 0 ? (size_t)CARRY_OUT_TOK * dk * sizeof(float) : 0);
+        if (co_smem > 48 * 1024) {
+            cudaError_t e = cudaFuncSetAttribute(recurrence_carry_out_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)co_smem);
+            if (e != cudaSuccess) return (int)e;
+        }
+        odin_launch(recurrence_carry_out_kernel, dim3(n_items, H, (dv + 31) / 32), dim3(256), co_smem, s, p);
         ODIN_LAUNCH_CHECK();
     }
     return 0;
