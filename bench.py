@@ -822,7 +822,7 @@ def nikonex_kernels(z: dict, T: int, peaks: dict) -> dict:
     qkvg = torch.randn(T, RH * (2 * dk + 2 * dv), device=dev)
     rq, rk, rv, rg = qkvg[:, :RH * dk], qkvg[:, RH * dk:2 * RH * dk], qkvg[:, 2 * RH * dk:2 * RH * dk + RH * dv], qkvg[:, 2 * RH * dk + RH * dv:]
     ro = torch.empty(T, RH * dv, device=dev)
-    decay = torch.full((RH * dk,), 0.99, device=dev)
+    decay = torch.full((RH,), 0.99, device=dev)
     c0, c1 = torch.randn(RH * dk, device=dev) - 2, torch.rand(RH * dk, device=dev)
     cr, sr = torch.randn(max(T, ctx + 1), dk // 2, device=dev), torch.randn(max(T, ctx + 1), dk // 2, device=dev)
     both = qkvg[:, :2 * RH * dk]

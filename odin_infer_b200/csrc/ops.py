@@ -457,7 +457,7 @@ def linear_recurrence(mode: str, q: torch.Tensor, k: torch.Tensor | None, g: tor
 
     "bonus": w = exp(-exp(g + c0)); o = (S + diag(c1) k v^T)^T q; S = diag(w) S + k v^T
     "gated": f = c1 + (1 - c1) sigmoid(g + c0); S = diag(f) S + (1 - f) v^T; o = S^T silu(q)
-    "fixed": S = diag(c0) S + k v^T; o = S^T q (a constant decay per head and key channel; g and c1 unused)
+    "fixed": S = c0 S + k v^T; o = S^T q (one constant decay per head, c0: [H]; g and c1 unused)
 
     q, k, g: float32 [T, H dk] (strided views are fine), v, out: float32 [T, H dv].
     shift_src / shift_state: after the walk the last row of shift_src of every sequence is stored
@@ -473,7 +473,8 @@ def linear_recurrence(mode: str, q: torch.Tensor, k: torch.Tensor | None, g: tor
     for t in (q, g, v, out) + ((k,) if k is not None else ()):
         assert t.dtype == torch.float32 and t.stride(1) == 1
     assert state.dtype == torch.float32 and state.stride(1) == 1 and c0.dtype == c1.dtype
-    assert c0.numel() == n_heads * dk and c1.numel() == n_heads * dk
+    per = n_heads if mode == "fixed" else n_heads * dk
+    assert c0.numel() == per and c1.numel() == per
     kk = k if k is not None else q
     width = 0
     if shift_src is not None:

@@ -77,7 +77,7 @@ extern "C" int odin_token_shift(const void* h, int dtype, const float* state, lo
 // ------------------------------------------------------------ the recurrence
 #define REC_BONUS 0   // o = (S + diag(u) k v^T)^T r, then S = diag(w) S + k v^T, w = exp(-exp(raw + w0))
 #define REC_GATED 1   // f = l + (1 - l) sigmoid(raw + b); S = diag(f) S + (1 - f) v^T; o = S^T silu(q)
-#define REC_FIXED 2   // S = diag(c0) S + k v^T; o = S^T q: a decay that is a constant per (head, key channel)
+#define REC_FIXED 2   // S = c0 S + k v^T; o = S^T q: a decay that is one constant per head (c0: [H])
 // Threads that share a column of S: each owns a quarter of the key channels.  (Sixteen lanes per column, a quarter of
 // the registers each, walked a prompt of 2,048 tokens a fifth faster and made a decode step three to four times slower:
 // four times the threads for the same work.)
@@ -89,7 +89,7 @@ struct RecParams {
     const float* k; long long k_stride;   // REC_BONUS and REC_FIXED
     const float* g; long long g_stride;   // the raw decay / forget gate (REC_FIXED: unused)
     const float* v; long long v_stride;   // [rows, H*dv]
-    VecRef c0, c1;                        // per (head, key channel): REC_BONUS w0 and u; REC_GATED bias and lower bound
+    VecRef c0, c1;                        // per (head, key channel): REC_BONUS w0 and u; REC_GATED bias and lower bound; REC_FIXED: c0 per head
     float* o; long long o_stride;         // [rows, H*dv]
     float* state; long long state_stride; // per slot: [H][dk][dv] floats
     const int* seq_start; const int* seq_slots;
@@ -125,6 +125,7 @@ linear_recurrence_kernel(RecParams p) {
     constexpr int NK = SL * REC_SPLIT;             // key channels the registers hold (dk <= NK)
     constexpr int TOK = NK > 128 ? 8 : 16;
     constexpr bool BONUS_IN_REGS = SL <= 32;
+    constexpr bool UNI = MODE == REC_FIXED;        // one decay for the whole head: a register, no row of shared memory
     // A warp's four parts read their channels at the same moment, SL floats apart: every part's channels sit four floats
     // further on than the part before, so that the four 16-byte reads fall into different banks (SL = 32: banks 0, 4, 8, 12
     // in place of four times bank 0).
@@ -148,14 +149,15 @@ linear_recurrence_kernel(RecParams p) {
     if (row1 <= row0) return;  // an empty (padding) sequence owns no state
     const bool owns = j < p.dv;
     const int i0 = part * SL;
-    float S[SL], ub[BONUS_IN_REGS ? SL : 1], D[BLOCKS ? SL : 1];
+    float S[SL], ub[BONUS_IN_REGS ? SL : 1], D[(BLOCKS && !UNI) ? SL : 1];
+    const float wuni = UNI ? p.c0.at(head) : 0.f;
     float* st = BLOCKS ? p.s_loc + ((size_t)blockIdx.x * p.H + head) * dk * p.dv + j
                        : p.state + (size_t)slot * p.state_stride + (size_t)head * dk * p.dv + j;
 #pragma unroll
     for (int i = 0; i < SL; ++i) S[i] = (!BLOCKS && owns && i0 + i < dk) ? st[(size_t)(i0 + i) * p.dv] : 0.f;
     if (BLOCKS) {
 #pragma unroll
-        for (int i = 0; i < SL; ++i) D[i] = 1.0f;
+        for (int i = 0; i < (UNI ? 1 : SL); ++i) D[i] = 1.0f;
     }
     const bool writes_qp = BLOCKS && cj == 0 && blockIdx.z == 0;   // one column's lanes write what is per key channel
     __syncthreads();
@@ -200,7 +202,6 @@ linear_recurrence_kernel(RecParams p) {
                     } else if (MODE == REC_FIXED) {
                         qv = rq[f];
                         kv = rk[f];
-                        wv = p.c0.at(hc + i);
                     } else {
                         const float l = p.c1.at(hc + i);
                         const float fg = l + (1.0f - l) * (1.0f / (1.0f + expf(-(rg[f] + p.c0.at(hc + i)))));
@@ -210,7 +211,8 @@ linear_recurrence_kernel(RecParams p) {
                     }
                 }
                 const int ip = i + (i / SL) * 4;
-                sq[u][ip] = qv; sk[u][ip] = kv; sw[u][ip] = wv;
+                sq[u][ip] = qv; sk[u][ip] = kv;
+                if (!UNI) sw[u][ip] = wv;
             }
             if (e < nt * ccols) sv[e / ccols][e % ccols] = rv[f];
         }
@@ -226,11 +228,13 @@ linear_recurrence_kernel(RecParams p) {
         for (int u = 0; u < nt; ++u) {
             const float vj = sv[u][cj];
             float acc0 = 0.f, acc1 = 0.f;
+            if (BLOCKS && UNI) D[0] *= wuni;   // the output looks at the state after the token's own decay
 #pragma unroll
             for (int i4 = 0; i4 < SL; i4 += 4) {
                 const float4 k4 = *reinterpret_cast<const float4*>(&sk[u][i0 + part * 4 + i4]);
                 const float4 q4 = *reinterpret_cast<const float4*>(&sq[u][i0 + part * 4 + i4]);
-                const float4 w4 = *reinterpret_cast<const float4*>(&sw[u][i0 + part * 4 + i4]);
+                float4 w4 = make_float4(wuni, wuni, wuni, wuni);
+                if (!UNI) w4 = *reinterpret_cast<const float4*>(&sw[u][i0 + part * 4 + i4]);
                 const float kk[4] = {k4.x, k4.y, k4.z, k4.w}, qq[4] = {q4.x, q4.y, q4.z, q4.w}, ww[4] = {w4.x, w4.y, w4.z, w4.w};
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
@@ -239,10 +243,11 @@ linear_recurrence_kernel(RecParams p) {
                     if (BLOCKS) {
                         // q times the decays between the block's start and this token's look at the state:
                         // before its own decay where the output comes before the update, after it else
-                        if (MODE != REC_BONUS) D[BLOCKS ? i : 0] *= ww[e];
+                        constexpr int di = (BLOCKS && !UNI) ? 1 : 0;   // D[i * di]: the channel's own product, or the head's one
+                        if (MODE != REC_BONUS && !UNI) D[i * di] *= ww[e];
                         if (writes_qp && i0 + i < dk)
-                            p.qp[(size_t)(t0 + u) * p.H * dk + hc + i0 + i] = qq[e] * D[BLOCKS ? i : 0];
-                        if (MODE == REC_BONUS) D[BLOCKS ? i : 0] *= ww[e];
+                            p.qp[(size_t)(t0 + u) * p.H * dk + hc + i0 + i] = qq[e] * D[i * di];
+                        if (MODE == REC_BONUS) D[i * di] *= ww[e];
                     }
                     if (MODE == REC_BONUS) {
                         const float bonus = BONUS_IN_REGS ? ub[BONUS_IN_REGS ? i : 0] : sb[i0 + i];
@@ -267,7 +272,7 @@ linear_recurrence_kernel(RecParams p) {
     if (writes_qp) {
 #pragma unroll
         for (int i = 0; i < SL; ++i)
-            if (i0 + i < dk) p.d_tot[(size_t)blockIdx.x * p.H * dk + hc + i0 + i] = D[BLOCKS ? i : 0];
+            if (i0 + i < dk) p.d_tot[(size_t)blockIdx.x * p.H * dk + hc + i0 + i] = D[(BLOCKS && !UNI) ? i : 0];
     }
     if (head == 0 && blockIdx.z == 0 && p.shift_src != nullptr && row1 == seq_end) {
         float* dst = p.shift_state + (size_t)slot * p.shift_stride;

@@ -142,9 +142,8 @@ class Retention(Mixer):
             mats = [t.float() for t in mats]
         self.w_qkvg = torch.cat(mats, dim=0).contiguous()
         self.w_o = tensors[n["o"]]
-        # the decay of every (head, key channel), rounded to 32-bit once
-        self.decay = torch.tensor(self.decay_values, dtype=torch.float64).to(torch.float32).repeat_interleave(self.D) \
-            .contiguous().to(rt.device)
+        # the heads' decays, rounded to 32-bit once
+        self.decay = torch.tensor(self.decay_values, dtype=torch.float64).to(torch.float32).contiguous().to(rt.device)
         self._dummy = torch.zeros(1, 1, dtype=torch.float32, device=rt.device)
 
     def state_bytes(self) -> int:
