@@ -152,6 +152,68 @@ heads_linear_kernel(const TA* __restrict__ a, size_t a_rs, size_t a_hs, const TW
         if (t0 + u < T) out[(size_t)(t0 + u) * o_rs + (size_t)h * o_hs + n] = from_f32<TO>(acc[u]);
 }
 
+// Many tokens: a CTA takes 64 tokens by 64 output channels of one head, K in steps of 32 through shared memory, a thread
+// four tokens by four channels.  Every output element is the same chain of multiply-adds over k ascending as in the
+// kernel above (channels beyond K add exact zeros), so the two give the same bits.
+#define HLT_TILE 64
+#define HLT_KC 32
+template <typename TA, typename TW, typename TO>
+__global__ void __launch_bounds__(256)
+heads_linear_tiled_kernel(const TA* __restrict__ a, size_t a_rs, size_t a_hs, const TW* __restrict__ w, TO* __restrict__ out,
+                          size_t o_rs, size_t o_hs, int T, int N, int K) {
+    __shared__ __align__(16) float As[HLT_KC][HLT_TILE + 4];   // [k][token]
+    __shared__ __align__(16) float Ws[HLT_KC][HLT_TILE];       // [k][channel]
+    pdl_trigger();
+    const int h = blockIdx.y, t0 = blockIdx.z * HLT_TILE, n0 = blockIdx.x * HLT_TILE;
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    const TW* wh = w + (size_t)h * K * N;
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+    pdl_wait();
+    for (int k0 = 0; k0 < K; k0 += HLT_KC) {
+        float ra[8], rw[8];
+#pragma unroll
+        for (int f = 0; f < 8; ++f) {
+            const int e = threadIdx.x + f * 256;
+            const int u = e / HLT_KC, k = e % HLT_KC;          // a: consecutive threads along k
+            ra[f] = (t0 + u < T && k0 + k < K) ? to_f32(a[(size_t)(t0 + u) * a_rs + (size_t)h * a_hs + k0 + k]) : 0.f;
+            const int kw = e / HLT_TILE, n = e % HLT_TILE;     // w: consecutive threads along the channels
+            rw[f] = (k0 + kw < K && n0 + n < N) ? to_f32(wh[(size_t)(k0 + kw) * N + n0 + n]) : 0.f;
+        }
+        __syncthreads();   // the step before has been read
+#pragma unroll
+        for (int f = 0; f < 8; ++f) {
+            const int e = threadIdx.x + f * 256;
+            As[e % HLT_KC][e / HLT_KC] = ra[f];
+            Ws[e / HLT_TILE][e % HLT_TILE] = rw[f];
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < HLT_KC; ++k) {
+            const float4 a4 = *reinterpret_cast<const float4*>(&As[k][ty * 4]);
+            const float4 w4 = *reinterpret_cast<const float4*>(&Ws[k][tx * 4]);
+            const float av[4] = {a4.x, a4.y, a4.z, a4.w}, wv[4] = {w4.x, w4.y, w4.z, w4.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(wv[j], av[i], acc[i][j]);
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int t = t0 + ty * 4 + i;
+        if (t >= T) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int n = n0 + tx * 4 + j;
+            if (n < N) out[(size_t)t * o_rs + (size_t)h * o_hs + n] = from_f32<TO>(acc[i][j]);
+        }
+    }
+}
+
 extern "C" int odin_heads_linear(const void* a, int a_dtype, long long a_rs, long long a_hs, const void* w, int w_dtype,
                                  void* out, int out_dtype, long long o_rs, long long o_hs, int T, int H, int N, int K,
                                  void* stream) {
@@ -161,9 +223,17 @@ extern "C" int odin_heads_linear(const void* a, int a_dtype, long long a_rs, lon
     if (smem > 48 * 1024 || (T + HL_TOK - 1) / HL_TOK > 65535) return ODIN_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
     const dim3 grid((unsigned)((N + HL_THREADS - 1) / HL_THREADS), (unsigned)H, (unsigned)((T + HL_TOK - 1) / HL_TOK));
+    const bool tiled = T >= 32 && (T + HLT_TILE - 1) / HLT_TILE <= 65535;
+    const dim3 tgrid((unsigned)((N + HLT_TILE - 1) / HLT_TILE), (unsigned)H, (unsigned)((T + HLT_TILE - 1) / HLT_TILE));
 #define GO(TA, TW, TO)                                                                                              \
-    odin_launch(heads_linear_kernel<TA, TW, TO>, grid, dim3(HL_THREADS), smem, s, (const TA*)a, (size_t)a_rs,       \
-                (size_t)a_hs, (const TW*)w, (TO*)out, (size_t)o_rs, (size_t)o_hs, T, N, K)
+    do {                                                                                                            \
+        if (tiled)                                                                                                  \
+            odin_launch(heads_linear_tiled_kernel<TA, TW, TO>, tgrid, dim3(256), 0, s, (const TA*)a, (size_t)a_rs,  \
+                        (size_t)a_hs, (const TW*)w, (TO*)out, (size_t)o_rs, (size_t)o_hs, T, N, K);                 \
+        else                                                                                                        \
+            odin_launch(heads_linear_kernel<TA, TW, TO>, grid, dim3(HL_THREADS), smem, s, (const TA*)a,             \
+                        (size_t)a_rs, (size_t)a_hs, (const TW*)w, (TO*)out, (size_t)o_rs, (size_t)o_hs, T, N, K);   \
+    } while (0)
     if (a_dtype == ODIN_BF16 && w_dtype == ODIN_BF16 && out_dtype == ODIN_BF16) GO(bf16, bf16, bf16);
     else if (a_dtype == ODIN_F32 && w_dtype == ODIN_F32 && out_dtype == ODIN_F32) GO(float, float, float);
     else if (a_dtype == ODIN_F32 && w_dtype == ODIN_BF16 && out_dtype == ODIN_BF16) GO(float, bf16, bf16);

@@ -7,6 +7,7 @@
     python -m odin_infer_b200.csrc.microbench add-rmsnorm --rows 8 --width 4096 --split 4
     python -m odin_infer_b200.csrc.microbench linear-recurrence --tokens 2048 --heads 32 --head-dim 64 [--gated | --fixed]
                                                                   [--batch 8] [--block-len 128]
+    python -m odin_infer_b200.csrc.microbench heads-linear --tokens 2048 --heads 16 --k 64 --n 64
     python -m odin_infer_b200.csrc.microbench mma-rate
 
 Prints one JSON line: the median time and the achieved bytes/s and flop/s of the kernel's
@@ -56,7 +57,7 @@ def paged(batch: int, ctx: int, n_kv: int, hd: int):
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("kernel", choices=["gemm", "decode-attention", "prefill-attention", "add-rmsnorm", "head-prep",
-                                       "linear-recurrence", "mma-rate"])
+                                       "linear-recurrence", "heads-linear", "mma-rate"])
     ap.add_argument("--m", type=int, default=8)
     ap.add_argument("--n", type=int, default=24576)
     ap.add_argument("--k", type=int, default=4096)
@@ -104,6 +105,18 @@ def main(argv=None) -> int:
         nbytes = 4 * (T * H * (3 * dk + 2 * dv) + 2 * B * H * dk * dv)
         out.update(form=mode, sequences=B, tokens_each=T1, heads=H, key_channels=dk, value_channels=dv, us=round(ms * 1e3, 2),
                    gbs=round(nbytes / ms / 1e6, 1), gflops=round(5 * T * H * dk * dv / ms / 1e6, 1))
+        print(json.dumps(out))
+        return 0
+
+    if args.kernel == "heads-linear":
+        # --tokens rows of --heads heads: a product of --k input by --n output channels per head, between strided rows
+        T, H, K, N = args.tokens, args.heads, args.k, args.n
+        a = torch.randn(T, H * 2 * K, device=DEV).bfloat16()
+        w = (torch.randn(H, K, N, device=DEV) / K ** 0.5).bfloat16()
+        o = torch.empty(T, H * 2 * N, device=DEV, dtype=torch.bfloat16)
+        ms = timeit(lambda: ops.heads_linear(a, 2 * K, w, o, 2 * N), args.iters)
+        out.update(tokens=T, heads=H, k=K, n=N, us=round(ms * 1e3, 2), gbs=round(2 * T * H * (K + N) / ms / 1e6, 1),
+                   gflops=round(2 * T * H * K * N / ms / 1e6, 1))
         print(json.dumps(out))
         return 0
 

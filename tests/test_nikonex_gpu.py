@@ -708,6 +708,27 @@ def test_a_product_per_head_and_the_unit_norm_with_its_gate(dtype, tol):
     close(y, want, tol)
 
 
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-6), (torch.bfloat16, 8e-3)])
+@pytest.mark.parametrize("T,H,K,N", [(200, 3, 37, 50), (64, 2, 64, 64), (33, 1, 130, 7), (321, 5, 8, 96)])
+def test_a_product_per_head_of_many_tokens_has_the_bits_of_few(dtype, tol, T, H, K, N):
+    """Many tokens go through tiles in shared memory, few through a kernel of their own: the same sums in the same order,
+    so a token's values do not depend on how many others come with it; and against float64, into a strided output."""
+    from odin_infer_b200.csrc import ops
+    torch.manual_seed(T + K)
+    a = torch.randn(T, H * (K + 3), device=DEV).to(dtype)
+    w = (torch.randn(H, K, N, device=DEV) / math.sqrt(K)).to(dtype)
+    out = torch.full((T, H * (N + 2)), 5.0, dtype=dtype, device=DEV)
+    ops.heads_linear(a, K + 3, w, out, N + 2)
+    want = torch.einsum("thk,hkn->thn", a.double().cpu().view(T, H, K + 3)[:, :, :K], w.double().cpu())
+    got = out.view(T, H, N + 2)
+    close(got[:, :, :N], want, tol)
+    assert (got[:, :, N:] == 5.0).all()   # what lies between the heads' outputs is left alone
+    few = torch.full_like(out, 5.0)
+    for t0 in range(0, T, 9):
+        ops.heads_linear(a[t0:t0 + 9], K + 3, w, few[t0:t0 + 9], N + 2)
+    assert torch.equal(out, few)
+
+
 @pytest.mark.parametrize("act", ["relu2", "silu", "gelu_tanh"])
 @pytest.mark.parametrize("E,K,N", [(3, 64, 40), (5, 72, 136), (2, 128, 256)])
 def test_grouped_product_without_a_gate_applies_its_activation_as_it_reads_back(act, E, K, N):
