@@ -20,6 +20,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import math
 import os
 import statistics
 import subprocess
@@ -697,7 +698,7 @@ def nikonex_config(z: dict) -> dict:
            "rot": {"dims": z["rot_dim"], "base": 500000.0,
                    "scaling": {"factor": 8.0, "original": 2048, "fast": 32.0, "slow": 1.0}}}
     ret = {"heads": z["ret_heads"], "dim": z["ret_dim"], "vdim": z["ret_v"],
-           "decay": [1.0 - 2.0 ** (-5.0 - 6.0 * i / max(z["ret_heads"] - 1, 1)) for i in range(z["ret_heads"])],
+           "decay": [math.exp(-1.0 / (8.0 * 2.0 ** (8.0 * i / max(z["ret_heads"] - 1, 1)))) for i in range(z["ret_heads"])],  # memories of 8 to 2,048 tokens
            "rot": {"dims": z["ret_dim"], "base": 500000.0}}
     moe = {"kind": "moe", "expert": {"ff": z["eff"]}, "shared": {"ff": z["shared"]},
            "router": {"experts": z["experts"], "top": z["top"], "scale": 2.5, "groups": {"count": z["groups"], "keep": z["keep"]}}}

@@ -95,7 +95,7 @@ def main(argv=None) -> int:
         v, o = torch.randn(T, H * dv, device=DEV), torch.empty(T, H * dv, device=DEV)
         c0, c1 = torch.randn(H * dk, device=DEV).bfloat16() - 2, torch.rand(H * dk, device=DEV).bfloat16()
         if mode == "fixed":
-            c0 = c1 = (1.0 - 2.0 ** (-5.0 - 6.0 * torch.arange(H, device=DEV) / max(H - 1, 1))).contiguous()
+            c0 = c1 = torch.exp(-1.0 / (8.0 * 2.0 ** (8.0 * torch.arange(H, device=DEV) / max(H - 1, 1)))).contiguous()  # memories of 8 to 2,048 tokens
         state = torch.zeros(B, H * dk * dv, device=DEV)
         starts = torch.arange(0, T + 1, T1, dtype=torch.int32, device=DEV)
         slots = torch.arange(B, dtype=torch.int32, device=DEV)

@@ -82,7 +82,7 @@ def test_the_model_description_names_every_tensor_once():
 
 
 def test_shared_rows_have_one_storage_and_a_group_of_their_own():
-    cache = CacheManager(max_tokens=640, max_seq_len=320)
+    cache = CacheManager(max_tokens=768, max_seq_len=384)
     a = cache.add_entry(KVRequest(1, 48, 37, 0, 0, True), 0)
     b = cache.add_entry(KVRequest(1, 48, 37), 0)
     c = cache.add_entry(KVRequest(1, 48, 37, 0, 0, True), 128)

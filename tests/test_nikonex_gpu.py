@@ -730,7 +730,7 @@ def test_a_product_per_head_of_many_tokens_has_the_bits_of_few(dtype, tol, T, H,
 
 
 @pytest.mark.parametrize("act", ["relu2", "silu", "gelu_tanh"])
-@pytest.mark.parametrize("E,K,N", [(3, 64, 40), (5, 72, 136), (2, 128, 256)])
+@pytest.mark.parametrize("E,K,N", [(3, 64, 40), (5, 72, 152), (2, 128, 256)])
 def test_grouped_product_without_a_gate_applies_its_activation_as_it_reads_back(act, E, K, N):
     """Sorted rows times their tile's own expert on the tensor cores, act(a W^T) written in bfloat16: against a loop in
     float64, over an expert without a tile, an output that is no multiple of the tile and a K that is no multiple of 64."""
