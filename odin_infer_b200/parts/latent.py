@@ -32,6 +32,9 @@ class LatentAttention(Mixer):
                  names: dict, position_encoding: str | None, eps: float, scale: float, window: int = 0):
         if min(width, n_heads, head_dim, v_head_dim, q_rank, kv_rank) <= 0 or rot_dim < 0 or rot_dim % 2:
             raise ValueError("latent attention needs positive sizes and an even rot_dim")
+        if kv_rank + rot_dim > 512:
+            raise ValueError(f"latent attention: a cached row of kv_rank + rot_dim = {kv_rank + rot_dim} elements is more than "
+                             "the attention kernels take (512)")
         if rot_dim and position_encoding is None:
             raise ValueError("latent attention with a rotated part needs a position encoding")
         self.width, self.H, self.e, self.r, self.ev = width, n_heads, head_dim, rot_dim, v_head_dim
