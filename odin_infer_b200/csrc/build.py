@@ -29,6 +29,7 @@ GROUPS = {
     "elementwise": ["elementwise.cu"],
     "rowwise": ["rowwise.cu"],
     "recurrent": ["recurrent.cu"],
+    "state_space": ["state_space.cu"],
     "moe": ["moe.cu"],
     "moe_tc": ["moe_tc.cu"],
     "latent": ["latent.cu"],

@@ -37,6 +37,69 @@ extern "C" int odin_embed(const void* table, int table_dtype, const int* ids, fl
     return 0;
 }
 
+// ---------------------------------------------------------------- embedding plus a hashed pair of tokens
+// out[t] = table[ids[t]] + pair[(prev * mul_prev + ids[t] * mul_cur) mod buckets], prev the token before in the sequence: the
+// row above or, for a sequence's first row of this step, what its state holds (token + 1; 0: the sequence starts here, and
+// the pair table's row `buckets` stands in).  A second kernel stores every sequence's last token of the step in its state.
+template <typename TW>
+__global__ void embed_pair_kernel(const TW* __restrict__ table, const TW* __restrict__ pair, const int* __restrict__ ids,
+                                  const int* __restrict__ tok_seq, const int* __restrict__ seq_start,
+                                  const int* __restrict__ seq_slots, const int* __restrict__ state, size_t state_stride,
+                                  int buckets, long long mul_prev, long long mul_cur, float* __restrict__ out, int d, int V,
+                                  float scale) {
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int seq = tok_seq[t];
+    float* o = out + (size_t)t * d;
+    const int id = ids[t];
+    if (seq < 0 || id < 0 || id >= V) {
+        for (int j = threadIdx.x; j < d; j += blockDim.x) o[j] = 0.f;
+        return;
+    }
+    const int before = t > seq_start[seq] ? ids[t - 1] + 1 : state[(size_t)seq_slots[seq] * state_stride];
+    long long rowp = buckets;
+    if (before > 0) rowp = (((long long)(before - 1) * mul_prev + (long long)id * mul_cur) % buckets + buckets) % buckets;
+    const TW* row = table + (size_t)id * d;
+    const TW* prow = pair + (size_t)rowp * d;
+    for (int j = threadIdx.x; j < d; j += blockDim.x) o[j] = to_f32(row[j]) * scale + to_f32(prow[j]);
+}
+
+__global__ void store_last_token_kernel(const int* __restrict__ ids, const int* __restrict__ seq_start,
+                                        const int* __restrict__ seq_slots, int* __restrict__ state, size_t state_stride,
+                                        int n_seqs) {
+    pdl_trigger();
+    pdl_wait();
+    const int b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= n_seqs) return;
+    const int r0 = seq_start[b], r1 = seq_start[b + 1];
+    if (r1 > r0) state[(size_t)seq_slots[b] * state_stride] = ids[r1 - 1] + 1;
+}
+
+extern "C" int odin_embed_pair(const void* table, const void* pair, int table_dtype, const int* ids, const int* tok_seq,
+                               const int* seq_start, const int* seq_slots, int* state, long long state_stride, int n_seqs,
+                               int buckets, long long mul_prev, long long mul_cur, float* out, int T, int d, int V,
+                               float scale, void* stream) {
+    if (T <= 0) return 0;
+    if (buckets <= 0 || n_seqs <= 0) return ODIN_ERR_BAD_ARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int threads = d >= 1024 ? 256 : 128;
+    if (table_dtype == ODIN_BF16)
+        odin_launch(embed_pair_kernel<bf16>, dim3(T), dim3(threads), 0, s, (const bf16*)table, (const bf16*)pair, ids, tok_seq,
+                    seq_start, seq_slots, (const int*)state, (size_t)state_stride, buckets, mul_prev, mul_cur, out, d, V, scale);
+    else if (table_dtype == ODIN_F32)
+        odin_launch(embed_pair_kernel<float>, dim3(T), dim3(threads), 0, s, (const float*)table, (const float*)pair, ids,
+                    tok_seq, seq_start, seq_slots, (const int*)state, (size_t)state_stride, buckets, mul_prev, mul_cur, out, d,
+                    V, scale);
+    else
+        return ODIN_ERR_UNSUPPORTED;
+    ODIN_LAUNCH_CHECK();
+    odin_launch(store_last_token_kernel, dim3((n_seqs + 127) / 128), dim3(128), 0, s, ids, seq_start, seq_slots, state,
+                (size_t)state_stride, n_seqs);
+    ODIN_LAUNCH_CHECK();
+    return 0;
+}
+
 // ------------------------------------------------- residual add + RMSNorm
 // One block per output row.  x_new = x + sum_s delta[s] (32-bit), written
 // back to x when there is no row gather; out = w * (r * x_new).

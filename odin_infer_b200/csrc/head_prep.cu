@@ -20,7 +20,9 @@
 // split product are added first, in order).  T: element type of q_out and of the cache.
 // bias: one value per column of the projection, added first (null: none).  norm_mode 0: no norm;
 // 1: RMSNorm with a weight before the rotation; 2: division by the root mean square after the
-// rotation, no weight.  vd: size of a value head (key and query heads have hd).
+// rotation, no weight; 3: RMSNorm over the whole q projection (all query heads of the token at once; likewise k) with weights
+// of that size, before the rotation.  vd: size of a value head (key and query heads have hd).
+// pairs: the rotation pairs element 2i with 2i + 1 instead of i with i + rot/2.
 template <typename TI, typename T>
 __global__ void __launch_bounds__(HP_WARPS * 32)
 head_prep_kernel(const TI* qkv, int n_split, size_t split_stride, T* q_out,  // may alias: no restrict
@@ -28,7 +30,7 @@ head_prep_kernel(const TI* qkv, int n_split, size_t split_stride, T* q_out,  // 
                  VecRef kw, int norm_mode, float eps, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                  int rot, int table_len, const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
                  const int* __restrict__ block_table, int bt_stride, T* __restrict__ k_cache,
-                 T* __restrict__ v_cache, int page_size, int write_kv) {
+                 T* __restrict__ v_cache, int page_size, int write_kv, int pairs) {
     __shared__ float buf[HP_WARPS][HP_MAX_HD];
     pdl_trigger();
     pdl_wait();
@@ -78,6 +80,26 @@ head_prep_kernel(const TI* qkv, int n_split, size_t split_stride, T* q_out,  // 
         const float r = 1.0f / sqrtf(ss);
         const VecRef& w = is_q ? qw : kw;
         for (int j = lane; j < hd; j += 32) b[j] = w.at(j) * (r * b[j]);
+    } else if (norm_mode == 3) {
+        // the sum of squares of the whole projection of this token, in an order that its size alone fixes (every warp of
+        // the token's q heads, or k heads, forms the same sum)
+        const int whole = (is_q ? Hq : Hkv) * hd;
+        const size_t wcol0 = is_q ? 0 : (size_t)Hq * hd;
+        const TI* wsrc = qkv + (size_t)t * row_stride + wcol0;
+        float sw = 0.f;
+        for (int j = lane; j < whole; j += 32) {
+            float v = to_f32(wsrc[j]);
+            for (int sp = 1; sp < n_split; ++sp) v += to_f32(wsrc[(size_t)sp * split_stride + j]);
+            if (bias.p != nullptr) v += bias.at((int)wcol0 + j);
+            sw += v * v;
+        }
+        sw = warp_sum(sw);
+        sw /= (float)whole;
+        sw += eps;
+        const float r = 1.0f / sqrtf(sw);
+        const VecRef& w = is_q ? qw : kw;
+        const int w0 = (is_q ? head : kvh) * hd;
+        for (int j = lane; j < hd; j += 32) b[j] = w.at(w0 + j) * (r * b[j]);
     }
     __syncwarp();
     const int half = rot >> 1;
@@ -88,7 +110,12 @@ head_prep_kernel(const TI* qkv, int n_split, size_t split_stride, T* q_out,  // 
     for (int e = 0; e < HP_MAX_HD / 32; ++e) {
         const int j = lane + 32 * e;
         if (j >= hd) break;
-        if (j < rot && in_table) {
+        if (j < rot && in_table && pairs) {
+            const int i = j >> 1;
+            const float c = cos_t[(size_t)pos * half + i], s = sin_t[(size_t)pos * half + i];
+            const float x = b[2 * i], y = b[2 * i + 1];
+            o[e] = (j & 1) ? (x * s + y * c) : (x * c - y * s);
+        } else if (j < rot && in_table) {
             const int i = (j < half) ? j : j - half;
             const float c = cos_t[(size_t)pos * half + i], s = sin_t[(size_t)pos * half + i];
             const float x = b[i], y = b[i + half];
@@ -279,13 +306,13 @@ extern "C" int odin_head_prep(const void* qkv, int in_dtype, int n_split, long l
                               const void* k_norm_w, int w_dtype, int norm_mode, float eps,
                               const float* cos_t, const float* sin_t, int rot, int table_len,
                               const int* tok_pos, const int* tok_seq, const int* block_table, int bt_stride,
-                              void* k_cache, void* v_cache, int page_size, int write_kv, void* stream) {
+                              void* k_cache, void* v_cache, int page_size, int write_kv, int pairs, void* stream) {
     if (T <= 0) return 0;
     if (hd > HP_MAX_HD || hd <= 0 || vd > HP_MAX_HD || vd <= 0 || (rot & 1) || rot > hd || rot < 0 || n_split < 1 ||
-        norm_mode < 0 || norm_mode > 2)
+        norm_mode < 0 || norm_mode > 3)
         return ODIN_ERR_UNSUPPORTED;
     const int has_norm = norm_mode == 1;
-    const bool plain_heads = bias == nullptr && norm_mode != 2 && vd == hd;
+    const bool plain_heads = bias == nullptr && norm_mode < 2 && vd == hd && !pairs;
     cudaStream_t s = (cudaStream_t)stream;
     const int n_heads = Hq + 2 * Hkv;
     dim3 grid(T, (n_heads + HP_WARPS - 1) / HP_WARPS);
@@ -323,7 +350,7 @@ extern "C" int odin_head_prep(const void* qkv, int in_dtype, int n_split, long l
     odin_launch(head_prep_kernel<TI, TT>, grid, dim3(HP_WARPS * 32), 0, s,                                           \
         (const TI*)qkv, n_split, (size_t)split_stride, (TT*)q_out, (size_t)q_out_stride, Hq, Hkv, hd, vd,           \
         (size_t)row_stride, bv, qw, kw, norm_mode, eps, cos_t, sin_t, rot, table_len, tok_pos, tok_seq, block_table,     \
-        (int)bt_stride, (TT*)k_cache, (TT*)v_cache, page_size, write_kv)
+        (int)bt_stride, (TT*)k_cache, (TT*)v_cache, page_size, write_kv, pairs)
     if (in_dtype == ODIN_BF16 && dtype == ODIN_BF16) GO(bf16, bf16);
     else if (in_dtype == ODIN_F32 && dtype == ODIN_F32) GO(float, float);
     else if (in_dtype == ODIN_F32 && dtype == ODIN_BF16) GO(float, bf16);

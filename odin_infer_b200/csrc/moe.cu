@@ -8,6 +8,10 @@
 //             is the sum of its two largest scores, only experts of the `keep` best groups can be chosen; the weights are
 //             the chosen scores divided by their sum (+ 1e-20), times `route_scale`.  With a gate row (row E of the
 //             router's matrix) the `always` rows are weighted by sigmoid(row E . h), which also goes to `gate_out`.
+//             score 2: the scores are the softmax over all rows of the router; an expert is chosen by score + correction (the
+//             bias), a group's score is its largest choice score, and the weights are the chosen experts' scores (without the
+//             correction) divided by their sum (+ 1e-20), times `route_scale`.  Rows from `n_real` on have no expert behind
+//             them: a token that chooses one gets its own input back, times the weight (summed per token into `pass_out`).
 //   gate|up:  a[r, j] = act(Wg[e_r] h_t)_j * (Wu[e_r] h_t)_j          r = t * rows_per_token + k
 //             (not gated: a[r, j] = act(Wu[e_r] h_t)_j)
 //   down:     y[k, t, :] = weight_r * Wd[e_r] a[r, :]                 32-bit, one slice per choice
@@ -96,10 +100,11 @@ __global__ void __launch_bounds__(1024)
 moe_router_kernel(const TH* __restrict__ h, size_t h_stride, const TW* __restrict__ w, VecRef bias, int E, int d, int top,
                   int always, const int* __restrict__ tok_seq, int* __restrict__ ids, float* __restrict__ wts,
                   const float* __restrict__ logits, int score, int groups, int keep, float route_scale, int gate_row,
-                  float* __restrict__ gate_out) {
+                  float* __restrict__ gate_out, int n_real, float* __restrict__ pass_out) {
     extern __shared__ float sm[];
     float* hrow = sm;       // d
     float* z = sm + d;      // E (+ 1 with a gate row)
+    float* sc = z + E + 1;  // E: score 2 keeps the scores beside the choice scores
     const int rows = E + (gate_row ? 1 : 0);
     pdl_trigger();
     const int t = blockIdx.x, per = top + always;
@@ -111,18 +116,19 @@ moe_router_kernel(const TH* __restrict__ h, size_t h_stride, const TW* __restric
             wts[(size_t)t * per + k] = 0.f;
         }
         if (gate_out != nullptr && threadIdx.x == 0) gate_out[t] = 0.f;
+        if (pass_out != nullptr && threadIdx.x == 0) pass_out[t] = 0.f;
         return;
     }
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
     if (logits != nullptr) {
         for (int e = threadIdx.x; e < rows; e += blockDim.x)
-            z[e] = logits[(size_t)t * rows + e] + (bias.p != nullptr && e < E ? bias.at(e) : 0.f);
+            z[e] = logits[(size_t)t * rows + e] + (bias.p != nullptr && e < E && score != 2 ? bias.at(e) : 0.f);
     } else {
         for (int i = threadIdx.x; i < d; i += blockDim.x) hrow[i] = to_f32(h[(size_t)t * h_stride + i]);
         __syncthreads();
         for (int e = warp; e < rows; e += n_warps) {
             const float s = warp_dot(w + (size_t)e * d, hrow, d, lane);
-            if (lane == 0) z[e] = s + (bias.p != nullptr && e < E ? bias.at(e) : 0.f);
+            if (lane == 0) z[e] = s + (bias.p != nullptr && e < E && score != 2 ? bias.at(e) : 0.f);
         }
     }
     __syncthreads();
@@ -166,6 +172,44 @@ moe_router_kernel(const TH* __restrict__ h, size_t h_stride, const TW* __restric
                 __syncwarp();
             }
         }
+        if (score == 2) {
+            // scores: the softmax over all rows; choice scores: score + correction (the bias); a group's score is its
+            // largest choice score; the groups that do not stay count as minus infinity
+            float m = -CUDART_INF_F;
+            for (int e = lane; e < E; e += 32) m = fmaxf(m, z[e]);
+            m = warp_max(m);
+            float tot = 0.f;
+            for (int e = lane; e < E; e += 32) { const float pe = expf(z[e] - m); sc[e] = pe; tot += pe; }
+            tot = warp_sum(tot);
+            for (int e = lane; e < E; e += 32) {
+                const float se = sc[e] / tot;
+                sc[e] = se;
+                z[e] = se + (bias.p != nullptr ? bias.at(e) : 0.f);
+            }
+            __syncwarp();
+            if (groups > 1) {
+                const int gsz = E / groups;
+                float gs = -CUDART_INF_F;
+                if (lane < groups)
+                    for (int e = lane * gsz; e < (lane + 1) * gsz; ++e) gs = fmaxf(gs, z[e]);
+                unsigned kept = 0u;
+                for (int k = 0; k < keep; ++k) {
+                    float best = gs;
+                    int best_g = lane < groups ? lane : 0x7fffffff;
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) {
+                        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+                        const int og = __shfl_xor_sync(0xffffffffu, best_g, o);
+                        if (ov > best || (ov == best && og < best_g)) { best = ov; best_g = og; }
+                    }
+                    if (best_g < groups) kept |= 1u << best_g;
+                    if (lane == best_g) gs = -CUDART_INF_F;
+                }
+                for (int e = lane; e < E; e += 32)
+                    if (!((kept >> (e / gsz)) & 1u)) z[e] = -CUDART_INF_F;
+                __syncwarp();
+            }
+        }
         // `top` rounds of a warp-wide arg max; the chosen logit is taken out by -inf
         float chosen = 0.f, first = 0.f, sum = 0.f;
         int chosen_id = -1;
@@ -183,18 +227,24 @@ moe_router_kernel(const TH* __restrict__ h, size_t h_stride, const TW* __restric
                 if (ov > best || (ov == best && oe < best_e)) { best = ov; best_e = oe; }
             }
             if (k == 0) first = best;
-            const float p = score == 1 ? best : expf(best - first);
+            const float p = score == 1 ? best : score == 2 ? (best_e < E ? sc[best_e] : 0.f) : expf(best - first);
             sum += p;
             if (lane == k) { chosen = p; chosen_id = best_e; }
             if (lane == 0 && best_e < E) z[best_e] = -CUDART_INF_F;
             __syncwarp();
         }
+        // rows from n_real on have no expert behind them: their weights are summed into pass_out (the token's input is
+        // handed through that many times) and their places name no expert
+        const float wt = score != 0 ? chosen / (sum + 1e-20f) * route_scale : chosen / sum;
+        const bool passes = lane < top && chosen_id >= n_real && chosen_id < E;
+        const float passed = warp_sum(passes ? wt : 0.f);
+        if (pass_out != nullptr && lane == 0) pass_out[t] = passed;
         if (lane < top) {
-            ids[(size_t)t * per + lane] = chosen_id < E ? chosen_id : -1;
-            wts[(size_t)t * per + lane] = score == 1 ? chosen / (sum + 1e-20f) * route_scale : chosen / sum;
+            ids[(size_t)t * per + lane] = chosen_id < n_real ? chosen_id : -1;
+            wts[(size_t)t * per + lane] = passes ? 0.f : wt;
         }
         for (int k = lane; k < always; k += 32) {
-            ids[(size_t)t * per + top + k] = E + k;
+            ids[(size_t)t * per + top + k] = n_real + k;
             wts[(size_t)t * per + top + k] = always_w;
         }
     }
@@ -203,13 +253,13 @@ moe_router_kernel(const TH* __restrict__ h, size_t h_stride, const TW* __restric
 extern "C" int odin_moe_router(const void* h, int h_dtype, long long h_stride, const void* w, int w_dtype, const void* bias,
                                int bias_dtype, int T, int E, int d, int top, int always, const int* tok_seq, int* ids,
                                float* wts, const float* logits, int score, int groups, int keep, float route_scale,
-                               int gate_row, float* gate_out, void* stream) {
+                               int gate_row, float* gate_out, int n_real, float* pass_out, void* stream) {
     if (T <= 0) return 0;
     if (E <= 0 || top <= 0 || top > 32 || top > E || always < 0 || d <= 0) return ODIN_ERR_UNSUPPORTED;
-    if (score != 0 && score != 1) return ODIN_ERR_BAD_ARG;
+    if (score < 0 || score > 2 || n_real < 0 || n_real > E || (n_real < E && pass_out == nullptr)) return ODIN_ERR_BAD_ARG;
     if (groups < 1 || groups > 32 || E % groups != 0 || keep < 1 || keep > groups || (long long)keep * (E / groups) < top)
         return ODIN_ERR_UNSUPPORTED;
-    const size_t smem = (size_t)(d + E + 1) * sizeof(float);
+    const size_t smem = (size_t)(d + 2 * E + 1) * sizeof(float);
     if (smem > 200 * 1024) return ODIN_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
     VecRef bv{bias, bias_dtype == ODIN_BF16};
@@ -223,7 +273,7 @@ extern "C" int odin_moe_router(const void* h, int h_dtype, long long h_stride, c
             cudaFuncSetAttribute(moe_router_kernel<TH, TW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
         odin_launch(moe_router_kernel<TH, TW>, dim3(T), dim3(threads), smem, s, (const TH*)h, (size_t)h_stride,      \
                     (const TW*)w, bv, E, d, top, always, tok_seq, ids, wts, logits, score, groups, keep,             \
-                    route_scale, gate_row, gate_out);                                                                \
+                    route_scale, gate_row, gate_out, n_real, pass_out);                                              \
     } while (0)
     if (h_dtype == ODIN_BF16 && w_dtype == ODIN_BF16) GO(bf16, bf16);
     else if (h_dtype == ODIN_F32 && w_dtype == ODIN_F32) GO(float, float);

@@ -84,6 +84,23 @@ def embed(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, scale: floa
         c_int(table.shape[0]), c_float(scale), _stream()), "embed")
 
 
+def embed_pair(table: torch.Tensor, pair: torch.Tensor, ids: torch.Tensor, tok_seq: torch.Tensor, seq_start: torch.Tensor,
+               seq_slots: torch.Tensor, state: torch.Tensor, n_seqs: int, buckets: int, mul_prev: int, mul_cur: int,
+               out: torch.Tensor, scale: float = 1.0) -> None:
+    """out[t] = table[ids[t]] * scale + pair[(prev * mul_prev + ids[t] * mul_cur) mod buckets] as 32-bit floats, prev the
+    token before in the sequence: the row above, or what `state` (int32 [slots, >= 1], any row stride) holds for the
+    sequence's slot (token + 1; 0: the sequence starts here, and row `buckets` of `pair` stands in).  A second kernel
+    then stores every sequence's last token of this step in `state`.  Rows of sequence -1 become zeros."""
+    T, d = out.shape
+    assert out.dtype == torch.float32 and out.is_contiguous() and ids.dtype == torch.int32
+    assert table.shape[1] == d and tuple(pair.shape) == (buckets + 1, d) and pair.dtype == table.dtype
+    assert table.is_contiguous() and pair.is_contiguous() and state.dtype == torch.int32 and state.stride(1) == 1
+    _check(_fn("elementwise", "odin_embed_pair")(
+        _ptr(table), _ptr(pair), c_int(dtype_code(table.dtype)), _ptr(ids), _ptr(tok_seq), _ptr(seq_start), _ptr(seq_slots),
+        _ptr(state), c_longlong(state.stride(0)), c_int(n_seqs), c_int(buckets), c_longlong(mul_prev), c_longlong(mul_cur),
+        _ptr(out), c_int(T), c_int(d), c_int(table.shape[0]), c_float(scale), _stream()), "embed_pair", kernels=2)
+
+
 def add_rmsnorm(x: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor, eps: float,
                 out: torch.Tensor, rows: torch.Tensor | None = None) -> None:
     """x += sum of delta's leading splits (in place, 32-bit); out = RMSNorm(x) * weight.
@@ -275,17 +292,70 @@ def sigmoid_gate(o: torch.Tensor, gate: torch.Tensor, n_heads: int, v_head_dim: 
         c_int(v_head_dim), _stream()), "sigmoid_gate")
 
 
-def softcap(z: torch.Tensor, cap: float) -> None:
-    """z <- cap * tanh(z / cap) in place; z float32 [rows, n]."""
+def softcap(z: torch.Tensor, cap: float, scale: float = 1.0) -> None:
+    """z <- scale * cap * tanh(z / cap) in place (cap 0: z <- scale * z); z float32 [rows, n]."""
     assert z.dtype == torch.float32 and z.dim() == 2 and z.stride(1) == 1
     _check(_fn("rowwise", "odin_softcap")(_ptr(z), c_longlong(z.stride(0)), c_int(z.shape[0]), c_int(z.shape[1]),
-                                          c_float(cap), _stream()), "softcap")
+                                          c_float(cap), c_float(scale), _stream()), "softcap")
+
+
+class Term:
+    """One term of a combined update (see `combine_add`): `value` [n, d] or [parts, n, d] partial sums, times `scale`,
+    times row_scale[r] (float32 [n]) where given; with norm_weight ([d]) the summed row is first divided by its root mean
+    square (norm_eps inside the root) and multiplied by that weight."""
+
+    def __init__(self, value: torch.Tensor, scale: float = 1.0, row_scale: torch.Tensor | None = None,
+                 norm_weight: torch.Tensor | None = None, norm_eps: float = 0.0):
+        self.value, self.scale, self.row_scale = value, float(scale), row_scale
+        self.norm_weight, self.norm_eps = norm_weight, float(norm_eps)
+
+
+def combine_add(x: torch.Tensor | None, terms: list, post_weight: torch.Tensor | None = None, post_eps: float = 0.0,
+                next_weight: torch.Tensor | None = None, next_eps: float = 0.0, out: torch.Tensor | None = None,
+                rows: torch.Tensor | None = None, tok_seq: torch.Tensor | None = None) -> None:
+    """y = the sum of up to four `Term`s; x += post_weight * y / rms(y) (post_weight None: x += y), in place unless `rows`
+    gathers; then out = next_weight * x / rms(x) where next_weight is given.  x None: out (float32) = y.  Rows of sequence
+    -1 (tok_seq) are skipped.  All sums 32-bit, in an order that the width fixes."""
+    assert 0 < len(terms) <= 4
+    ref = x if x is not None else out
+    d = ref.shape[-1]
+    n_all = x.shape[0] if x is not None else out.shape[0]
+    n_rows = n_all if rows is None else rows.numel()
+    if x is not None:
+        assert x.dtype == torch.float32 and x.is_contiguous()
+    if out is not None:
+        assert out.is_contiguous() and tuple(out.shape) == (n_rows, d)
+    if rows is not None:
+        assert rows.dtype == torch.int32
+    n = len(terms)
+    ptrs, dts, nsp, sst, scl = (c_void_p * n)(), (c_int * n)(), (c_int * n)(), (c_longlong * n)(), (c_float * n)()
+    rsc, nws, nwd, nep = (c_void_p * n)(), (c_void_p * n)(), (c_int * n)(), (c_float * n)()
+    for i, t in enumerate(terms):
+        v = t.value
+        ns, st = _parts(v, n_all, d)
+        ptrs[i], dts[i], nsp[i], sst[i], scl[i] = _ptr(v), dtype_code(v.dtype), ns, st, t.scale
+        if t.row_scale is not None:
+            assert t.row_scale.dtype == torch.float32 and t.row_scale.is_contiguous() and t.row_scale.numel() == n_all
+        rsc[i] = _ptr(t.row_scale)
+        if t.norm_weight is not None:
+            assert t.norm_weight.numel() == d and t.norm_weight.is_contiguous()
+        nws[i], nwd[i] = _ptr(t.norm_weight), dtype_code(t.norm_weight.dtype) if t.norm_weight is not None else 0
+        nep[i] = t.norm_eps
+    for w in (post_weight, next_weight):
+        assert w is None or (w.numel() == d and w.is_contiguous())
+    _check(_fn("rowwise", "odin_combine_add")(
+        _ptr(x), c_int(n), ptrs, dts, nsp, sst, scl, rsc, nws, nwd, nep, _ptr(post_weight),
+        c_int(dtype_code(post_weight.dtype) if post_weight is not None else 0), c_float(post_eps), _ptr(next_weight),
+        c_int(dtype_code(next_weight.dtype) if next_weight is not None else 0), c_float(next_eps), _ptr(out),
+        c_int(dtype_code(out.dtype) if out is not None else 0), _ptr(rows), _ptr(tok_seq), c_int(n_rows), c_int(d),
+        _stream()), "combine_add")
 
 
 def moe_router(h: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None, top: int, always: int,
                tok_seq: torch.Tensor | None, ids: torch.Tensor, wts: torch.Tensor, logits: torch.Tensor | None = None,
                score: str = "softmax_of_chosen", groups: int = 1, keep: int = 1, route_scale: float = 1.0,
-               gate_row: bool = False, gate_out: torch.Tensor | None = None) -> None:
+               gate_row: bool = False, gate_out: torch.Tensor | None = None, n_real: int | None = None,
+               pass_out: torch.Tensor | None = None) -> None:
     """Per token: logits W h + bias in 32-bit, the `top` largest chosen, weights = softmax over the chosen logits;
     `always` further choices name the experts E, E + 1, ... with weight 1.  ids int32, wts float32: [T, top + always];
     rows of sequence -1 get expert -1.  logits: W h where a product has formed it already (float32 [T, rows of W]).
@@ -293,6 +363,11 @@ def moe_router(h: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None, top:
     score "sigmoid_in_groups": scores sigmoid(z); the experts form `groups` equal groups of neighbours, a group's score
     is the sum of its two largest scores, only experts of the `keep` best groups can be chosen (the `top` largest
     scores among them); weights = chosen scores / (their sum + 1e-20) * route_scale.
+    score "softmax_corrected_in_groups": scores softmax(z) over all rows; an expert is chosen by score + bias (a correction
+    that the weights do not see), a group's score is its largest choice score, weights = chosen scores / (their sum +
+    1e-20) * route_scale.  n_real: the first n_real rows of W have experts behind them; a token that chooses a later row
+    gets its own input back times that weight: such places name expert -1 with weight 0, and the token's summed weight of
+    them goes to pass_out (float32 [T]).  The `always` choices name the experts n_real, n_real + 1, ...
     gate_row: W has one row more than there are experts, g; the `always` choices are weighted by sigmoid(g . h),
     which also goes to gate_out (float32 [T]) where given."""
     T, d = h.shape
@@ -306,14 +381,18 @@ def moe_router(h: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None, top:
         assert logits.dtype == torch.float32 and logits.is_contiguous() and tuple(logits.shape) == (T, w.shape[0])
     if gate_out is not None:
         assert gate_row and gate_out.dtype == torch.float32 and gate_out.is_contiguous() and gate_out.numel() == T
+    n_real = E if n_real is None else n_real
+    if pass_out is not None:
+        assert pass_out.dtype == torch.float32 and pass_out.is_contiguous() and pass_out.numel() == T
     _check(_fn("moe", "odin_moe_router")(
         _ptr(h), c_int(dtype_code(h.dtype)), c_longlong(h.stride(0)), _ptr(w), c_int(dtype_code(w.dtype)), _ptr(bias),
         c_int(dtype_code(bias.dtype) if bias is not None else 0), c_int(T), c_int(E), c_int(d), c_int(top), c_int(always),
         _ptr(tok_seq), _ptr(ids), _ptr(wts), _ptr(logits), c_int(ROUTER_SCORES[score]), c_int(groups), c_int(keep),
-        c_float(route_scale), c_int(1 if gate_row else 0), _ptr(gate_out), _stream()), "moe_router")
+        c_float(route_scale), c_int(1 if gate_row else 0), _ptr(gate_out), c_int(n_real), _ptr(pass_out), _stream()),
+        "moe_router")
 
 
-ROUTER_SCORES = {"softmax_of_chosen": 0, "sigmoid_in_groups": 1}
+ROUTER_SCORES = {"softmax_of_chosen": 0, "sigmoid_in_groups": 1, "softmax_corrected_in_groups": 2}
 
 
 def moe_gate_up(h: torch.Tensor, w: torch.Tensor, ids: torch.Tensor, kind: str, out: torch.Tensor, gated: bool = True) -> None:
@@ -444,20 +523,23 @@ def token_shift(h: torch.Tensor, state: torch.Tensor, mu: torch.Tensor, out: tor
         c_int(T), c_int(d), _stream()), "token_shift")
 
 
-RECURRENCE_MODES = {"bonus": 0, "gated": 1, "fixed": 2}
+RECURRENCE_MODES = {"bonus": 0, "gated": 1, "fixed": 2, "gla": 3, "ssd": 4}
 
 
 def linear_recurrence(mode: str, q: torch.Tensor, k: torch.Tensor | None, g: torch.Tensor | None, v: torch.Tensor,
                       c0: torch.Tensor, c1: torch.Tensor, out: torch.Tensor, state: torch.Tensor,
                       seq_start: torch.Tensor, seq_slots: torch.Tensor, n_seqs: int, n_heads: int, dk: int, dv: int,
                       shift_src: torch.Tensor | None = None, shift_state: torch.Tensor | None = None,
-                      block_len: int = 0, max_new: int = 0) -> None:
+                      block_len: int = 0, max_new: int = 0, q_scale: float = 1.0, heads_per_group: int = 1) -> None:
     """The recurrence over a matrix-valued state per (sequence, head), S: [dk, dv] in `state`
     (float32 [slots, >= H dk dv], any row stride), sequence b's rows being seq_start[b] .. seq_start[b+1]:
 
     "bonus": w = exp(-exp(g + c0)); o = (S + diag(c1) k v^T)^T q; S = diag(w) S + k v^T
     "gated": f = c1 + (1 - c1) sigmoid(g + c0); S = diag(f) S + (1 - f) v^T; o = S^T silu(q)
     "fixed": S = c0 S + k v^T; o = S^T q (one constant decay per head, c0: [H]; g and c1 unused)
+    "gla":   w = sigmoid(g + c0)^c1 (as exp(c1 logsigmoid(g + c0))); S = diag(w) S + k v^T; o = S^T (q_scale q)
+    "ssd":   per head and token dt = softplus(g[t, head] + c1[head]), w = exp(-exp(c0[head]) dt) (g: [T, H], c0, c1: [H]);
+             S = w S + (dt k) v^T; o = S^T q; q and k are [T, (H / heads_per_group) dk]: heads_per_group heads share them
 
     q, k, g: float32 [T, H dk] (strided views are fine), v, out: float32 [T, H dv].
     shift_src / shift_state: after the walk the last row of shift_src of every sequence is stored
@@ -473,7 +555,7 @@ def linear_recurrence(mode: str, q: torch.Tensor, k: torch.Tensor | None, g: tor
     for t in (q, g, v, out) + ((k,) if k is not None else ()):
         assert t.dtype == torch.float32 and t.stride(1) == 1
     assert state.dtype == torch.float32 and state.stride(1) == 1 and c0.dtype == c1.dtype
-    per = n_heads if mode == "fixed" else n_heads * dk
+    per = n_heads if mode in ("fixed", "ssd") else n_heads * dk
     assert c0.numel() == per and c1.numel() == per
     kk = k if k is not None else q
     width = 0
@@ -496,7 +578,74 @@ def linear_recurrence(mode: str, q: torch.Tensor, k: torch.Tensor | None, g: tor
         _ptr(seq_start), _ptr(seq_slots), c_int(n_seqs), c_int(n_heads), c_int(dk), c_int(dv), _ptr(shift_src),
         c_int(dtype_code(shift_src.dtype) if shift_src is not None else 0), _ptr(shift_state),
         c_longlong(shift_state.stride(0) if shift_state is not None else 0), c_int(width), c_int(block_len),
-        c_int(n_blocks), _ptr(qp), _ptr(s_loc), _ptr(d_tot), _stream()), "linear_recurrence", kernels=kernels)
+        c_int(n_blocks), _ptr(qp), _ptr(s_loc), _ptr(d_tot), c_float(q_scale), c_int(heads_per_group), _stream()),
+        "linear_recurrence", kernels=kernels)
+
+
+def causal_conv(src: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, silu: bool, state: torch.Tensor,
+                tok_seq: torch.Tensor, seq_start: torch.Tensor, seq_slots: torch.Tensor, n_seqs: int, out: torch.Tensor) -> None:
+    """out[t, c] = act(bias[c] + sum_j weight[c, j] src[t - (taps - 1 - j), c]) over each sequence's rows (act: SiLU or
+    none); the rows before a step's first one come from `state` (float32 [slots, >= (taps - 1) C], any row stride: the
+    sequence's last taps - 1 inputs, oldest first; zeros at its start), into which a second kernel stores the step's last
+    inputs.  src: [T, C], a strided view is fine."""
+    T, C = out.shape
+    taps = weight.shape[1]
+    assert src.stride(1) == 1 and tuple(src.shape) == (T, C) and out.stride(1) == 1
+    assert weight.is_contiguous() and weight.shape[0] == C and state.dtype == torch.float32 and state.stride(1) == 1
+    assert state.shape[1] >= (taps - 1) * C
+    if bias is not None:
+        assert bias.numel() == C and bias.is_contiguous()
+    _check(_fn("state_space", "odin_causal_conv")(
+        _ptr(src), c_int(dtype_code(src.dtype)), c_longlong(src.stride(0)), _ptr(weight), c_int(dtype_code(weight.dtype)),
+        _ptr(bias), c_int(dtype_code(bias.dtype) if bias is not None else 0), c_int(taps), c_int(1 if silu else 0),
+        _ptr(state), c_longlong(state.stride(0)), _ptr(tok_seq), _ptr(seq_start), _ptr(seq_slots), c_int(n_seqs), _ptr(out),
+        c_int(dtype_code(out.dtype)), c_longlong(out.stride(0)), c_int(T), c_int(C), _stream()), "causal_conv",
+        kernels=2 if taps > 1 else 1)
+
+
+def selective_scan(x: torch.Tensor, dt: torch.Tensor, dt_bias: torch.Tensor | None, B: torch.Tensor, C: torch.Tensor,
+                   A_log: torch.Tensor, D: torch.Tensor | None, z: torch.Tensor | None, state: torch.Tensor,
+                   out: torch.Tensor, seq_start: torch.Tensor, seq_slots: torch.Tensor, n_seqs: int) -> None:
+    """Per channel c and state index n, over each sequence's rows in order: step = softplus(dt + dt_bias),
+    S[c, n] = exp(step_c A[c, n]) S[c, n] + step_c x_c B_n with A = -exp(A_log); out_c = (sum_n S[c, n] C_n + D_c x_c) *
+    silu(z_c).  x, z: [T, inner] in one element type (views are fine); dt float32 [T, inner]; B, C float32 [T, N] views of
+    one row stride; state float32 [slots, >= inner N], any row stride.  Everything inside is 32-bit."""
+    T, inner = out.shape
+    N = A_log.shape[1]
+    assert tuple(x.shape) == (T, inner) and x.stride(1) == 1 and dt.dtype == torch.float32 and dt.stride(1) == 1
+    assert B.dtype == C.dtype == torch.float32 and B.stride(0) == C.stride(0) and B.stride(1) == C.stride(1) == 1
+    assert tuple(B.shape) == tuple(C.shape) == (T, N) and A_log.is_contiguous() and A_log.shape[0] == inner
+    assert state.dtype == torch.float32 and state.stride(1) == 1 and state.shape[1] >= inner * N and out.stride(1) == 1
+    ws = [w for w in (A_log, D, dt_bias) if w is not None]
+    assert len({w.dtype for w in ws}) == 1 and all(w.is_contiguous() for w in ws)
+    if z is not None:
+        assert z.dtype == x.dtype and z.stride(1) == 1 and tuple(z.shape) == (T, inner)
+    _check(_fn("state_space", "odin_selective_scan")(
+        _ptr(x), c_int(dtype_code(x.dtype)), c_longlong(x.stride(0)), _ptr(dt), c_longlong(dt.stride(0)), _ptr(dt_bias),
+        _ptr(B), _ptr(C), c_longlong(B.stride(0)), _ptr(A_log), _ptr(D), c_int(dtype_code(A_log.dtype)), _ptr(z),
+        c_longlong(z.stride(0) if z is not None else 0), _ptr(state), c_longlong(state.stride(0)), _ptr(out),
+        c_int(dtype_code(out.dtype)), c_longlong(out.stride(0)), _ptr(seq_start), _ptr(seq_slots), c_int(n_seqs),
+        c_int(inner), c_int(N), _stream()), "selective_scan")
+
+
+def skip_gate_norm(o: torch.Tensor, x: torch.Tensor | None, D: torch.Tensor | None, head_dim: int, z: torch.Tensor | None,
+                   weight: torch.Tensor | None, groups: int, eps: float, out: torch.Tensor) -> None:
+    """out = weight * grouped_rms((o + D[head] x) * silu(z)): the row of `inner` elements (heads of head_dim) is cut into
+    `groups` equal consecutive parts, each divided by its own root mean square.  o float32 [T, inner] contiguous; x float32
+    view; z any view; D [heads] and weight [inner] of one element type; D (with x), z and weight are optional."""
+    T, inner = o.shape
+    assert o.dtype == torch.float32 and o.is_contiguous() and out.is_contiguous() and tuple(out.shape) == (T, inner)
+    if D is not None:
+        assert x is not None and x.dtype == torch.float32 and x.stride(1) == 1 and D.numel() * head_dim == inner
+    if weight is not None:
+        assert weight.numel() == inner and (D is None or D.dtype == weight.dtype)
+    zd = z.dtype if z is not None else torch.float32
+    wd = weight.dtype if weight is not None else (D.dtype if D is not None else torch.float32)
+    _check(_fn("state_space", "odin_skip_gate_norm")(
+        _ptr(o), _ptr(x if D is not None else None), c_longlong(x.stride(0) if D is not None else 0), _ptr(D),
+        c_int(head_dim), _ptr(z), c_int(dtype_code(zd)), c_longlong(z.stride(0) if z is not None else 0), _ptr(weight),
+        c_int(dtype_code(wd)), c_int(groups), c_float(eps), _ptr(out), c_int(dtype_code(out.dtype)), c_int(T), c_int(inner),
+        _stream()), "skip_gate_norm")
 
 
 def head_unit_scale(o: torch.Tensor, weight: torch.Tensor | None, per_head_weight: bool, gate: torch.Tensor | None,
@@ -732,12 +881,14 @@ def head_prep(qkv: torch.Tensor, n_q: int, n_kv: int, head_dim: int, q_norm: tor
               tok_pos: torch.Tensor, tok_seq: torch.Tensor, block_table: torch.Tensor,
               k_cache: torch.Tensor | None, v_cache: torch.Tensor | None, write_kv: bool = True,
               q_out: torch.Tensor | None = None, bias: torch.Tensor | None = None, unit_norm_after: bool = False,
-              v_head_dim: int | None = None) -> torch.Tensor:
+              v_head_dim: int | None = None, whole_norm: bool = False, pairs: bool = False) -> torch.Tensor:
     """Per-head RMSNorm and rotation of q and k, and the cache write of k and v.
 
     bias: one value per column of the projection, added first.  unit_norm_after: instead of the
     weighted norm before the rotation, q and k heads are divided by their root mean square after it
     (q_norm and k_norm are then None).  v_head_dim: size of a value head when it differs from head_dim.
+    whole_norm: the norm before the rotation runs over the token's whole q projection at once (and its whole k projection),
+    with q_norm [n_q head_dim] and k_norm [n_kv head_dim].  pairs: the rotation pairs element 2i with 2i + 1.
 
     qkv: [T, (n_q + 2 n_kv) head_dim], or float32 partial sums [parts, T, ...] of a split
     product (added first).  q goes to q_out ([T, n_q head_dim], of the cache's type); without
@@ -760,7 +911,10 @@ def head_prep(qkv: torch.Tensor, n_q: int, n_kv: int, head_dim: int, q_norm: tor
     has_norm = q_norm is not None
     if has_norm:
         assert k_norm is not None and q_norm.dtype == k_norm.dtype and not unit_norm_after
-        assert q_norm.numel() == head_dim and k_norm.numel() == head_dim
+        if whole_norm:
+            assert q_norm.numel() == n_q * head_dim and (n_kv == 0 or k_norm.numel() == n_kv * head_dim)
+        else:
+            assert q_norm.numel() == head_dim and k_norm.numel() == head_dim
     if bias is not None:
         assert bias.numel() == width and bias.is_contiguous()
     if write_kv:
@@ -774,11 +928,11 @@ def head_prep(qkv: torch.Tensor, n_q: int, n_kv: int, head_dim: int, q_norm: tor
         c_longlong(q_out.stride(0)), c_int(dtype_code(q_out.dtype)), c_int(T), c_int(n_q), c_int(n_kv),
         c_int(head_dim), c_int(vd), c_longlong(row_stride), _ptr(bias),
         c_int(dtype_code(bias.dtype) if bias is not None else 0), _ptr(q_norm), _ptr(k_norm),
-        c_int(dtype_code(q_norm.dtype) if has_norm else 0), c_int(2 if unit_norm_after else (1 if has_norm else 0)),
+        c_int(dtype_code(q_norm.dtype) if has_norm else 0), c_int(2 if unit_norm_after else ((3 if whole_norm else 1) if has_norm else 0)),
         c_float(eps),
         _ptr(cos), _ptr(sin), c_int(rotary_dim), c_int(cos.shape[0]), _ptr(tok_pos), _ptr(tok_seq),
         _ptr(block_table), c_int(block_table.stride(0)), _ptr(k_cache), _ptr(v_cache), c_int(PAGE),
-        c_int(1 if write_kv else 0), _stream()), "head_prep")
+        c_int(1 if write_kv else 0), c_int(1 if pairs else 0), _stream()), "head_prep")
     return q_out
 
 

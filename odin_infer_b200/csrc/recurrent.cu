@@ -78,6 +78,9 @@ extern "C" int odin_token_shift(const void* h, int dtype, const float* state, lo
 #define REC_BONUS 0   // o = (S + diag(u) k v^T)^T r, then S = diag(w) S + k v^T, w = exp(-exp(raw + w0))
 #define REC_GATED 1   // f = l + (1 - l) sigmoid(raw + b); S = diag(f) S + (1 - f) v^T; o = S^T silu(q)
 #define REC_FIXED 2   // S = c0 S + k v^T; o = S^T q: a decay that is one constant per head (c0: [H])
+#define REC_GLA 3     // w = sigmoid(raw + c0)^c1 = exp(c1 logsigmoid(raw + c0)); S = diag(w) S + k v^T; o = S^T (q_scale q)
+#define REC_SSD 4     // per head and token one step dt = softplus(raw[head] + c1[head]) and one decay w = exp(-exp(c0[head]) dt);
+                      // S = w S + (dt k) v^T; o = S^T q; q and k belong to the head's group (heads_per_group heads share them)
 // Threads that share a column of S: each owns a quarter of the key channels.  (Sixteen lanes per column, a quarter of
 // the registers each, walked a prompt of 2,048 tokens a fifth faster and made a decode step three to four times slower:
 // four times the threads for the same work.)
@@ -94,6 +97,8 @@ struct RecParams {
     float* state; long long state_stride; // per slot: [H][dk][dv] floats
     const int* seq_start; const int* seq_slots;
     int H, dk, dv;
+    float q_scale;        // REC_GLA: factor on q
+    int heads_per_group;  // REC_SSD: heads that share one q and one k (their columns: group * dk)
     // the token shift's memory: after the step the sequence's last row of h goes to its state
     const void* shift_src; int shift_is_bf16; float* shift_state; long long shift_stride; int width;
     // Blocks of tokens (block_len > 0): a CTA walks one block of one sequence from a state of zeros and leaves
@@ -143,6 +148,7 @@ linear_recurrence_kernel(RecParams p) {
     const int row1 = BLOCKS ? min(seq_end, row0 + p.block_len) : seq_end;
     const int slot = p.seq_slots[b];
     const int hc = head * dk;
+    const int qc = MODE == REC_SSD ? (head / p.heads_per_group) * dk : hc;   // the head's columns of q and k
     const int tok = max(1, min(TOK, REC_FETCH * (int)blockDim.x / NK));   // tokens per block: what the threads can fetch ahead
     for (int i = threadIdx.x; i < NK; i += blockDim.x) sb[i] = (MODE == REC_BONUS && i < dk) ? p.c1.at(hc + i) : 0.f;
     pdl_wait();
@@ -176,9 +182,10 @@ linear_recurrence_kernel(RecParams p) {
                 const int u = e / NK, i = e % NK;
                 if (i < dk) {
                     const size_t r = (size_t)(t0 + u);
-                    rq[f] = p.q[r * p.q_stride + hc + i];
-                    if (MODE != REC_FIXED) rg[f] = p.g[r * p.g_stride + hc + i];
-                    if (MODE != REC_GATED) rk[f] = p.k[r * p.k_stride + hc + i];
+                    rq[f] = p.q[r * p.q_stride + qc + i];
+                    if (MODE == REC_SSD) rg[f] = p.g[r * p.g_stride + head];
+                    else if (MODE != REC_FIXED) rg[f] = p.g[r * p.g_stride + hc + i];
+                    if (MODE != REC_GATED) rk[f] = p.k[r * p.k_stride + qc + i];
                 }
             }
             if (e < nt * ccols) {
@@ -202,6 +209,18 @@ linear_recurrence_kernel(RecParams p) {
                     } else if (MODE == REC_FIXED) {
                         qv = rq[f];
                         kv = rk[f];
+                    } else if (MODE == REC_GLA) {
+                        const float z = rg[f] + p.c0.at(hc + i);
+                        const float logsig = fminf(z, 0.f) - log1pf(expf(-fabsf(z)));
+                        qv = rq[f] * p.q_scale;
+                        kv = rk[f];
+                        wv = expf(p.c1.at(hc + i) * logsig);
+                    } else if (MODE == REC_SSD) {
+                        const float z = rg[f] + p.c1.at(head);
+                        const float dt = fmaxf(z, 0.f) + log1pf(expf(-fabsf(z)));
+                        qv = rq[f];
+                        kv = rk[f] * dt;
+                        wv = expf(-expf(p.c0.at(head)) * dt);
                     } else {
                         const float l = p.c1.at(hc + i);
                         const float fg = l + (1.0f - l) * (1.0f / (1.0f + expf(-(rg[f] + p.c0.at(hc + i)))));
@@ -409,13 +428,15 @@ extern "C" int odin_linear_recurrence(int mode, const float* q, long long q_stri
                                       float* state, long long state_stride, const int* seq_start, const int* seq_slots,
                                       int n_seqs, int H, int dk, int dv, const void* shift_src, int shift_dtype,
                                       float* shift_state, long long shift_stride, int width, int block_len, int n_blocks,
-                                      float* qp, float* s_loc, float* d_tot, void* stream) {
+                                      float* qp, float* s_loc, float* d_tot, float q_scale, int heads_per_group,
+                                      void* stream) {
     if (n_seqs <= 0) return 0;
     if (block_len < 0 || (block_len > 0 && (n_blocks <= 0 || qp == nullptr || s_loc == nullptr || d_tot == nullptr ||
                                             (long long)n_seqs * n_blocks > 2147483647LL)))
         return ODIN_ERR_BAD_ARG;
     if (H <= 0 || dk <= 0 || dk > REC_MAX_DK || dv <= 0 || dv > 256 || H > 65535) return ODIN_ERR_UNSUPPORTED;
-    if (mode != REC_BONUS && mode != REC_GATED && mode != REC_FIXED) return ODIN_ERR_BAD_ARG;
+    if (mode < REC_BONUS || mode > REC_SSD) return ODIN_ERR_BAD_ARG;
+    if (mode == REC_SSD && (heads_per_group <= 0 || H % heads_per_group != 0)) return ODIN_ERR_BAD_ARG;
     RecParams p;
     p.q = q; p.q_stride = q_stride; p.k = k; p.k_stride = k_stride; p.g = g; p.g_stride = g_stride;
     p.v = v; p.v_stride = v_stride;
@@ -425,6 +446,7 @@ extern "C" int odin_linear_recurrence(int mode, const float* q, long long q_stri
     p.shift_src = shift_src; p.shift_is_bf16 = shift_dtype == ODIN_BF16; p.shift_state = shift_state;
     p.shift_stride = shift_stride; p.width = width;
     p.block_len = block_len; p.n_blocks = n_blocks; p.qp = qp; p.s_loc = s_loc; p.d_tot = d_tot;
+    p.q_scale = q_scale; p.heads_per_group = heads_per_group > 0 ? heads_per_group : 1;
     const bool blocks = block_len > 0;
     const int n_items = blocks ? n_seqs * n_blocks : n_seqs;
     cudaStream_t s = (cudaStream_t)stream;
@@ -444,6 +466,10 @@ extern "C" int odin_linear_recurrence(int mode, const float* q, long long q_stri
         else if (mode == REC_BONUS) odin_launch(linear_recurrence_kernel<SL, REC_BONUS, false>, grid, dim3(threads), 0, s, p);     \
         else if (mode == REC_FIXED && blocks) odin_launch(linear_recurrence_kernel<SL, REC_FIXED, true>, grid, dim3(threads), 0, s, p);  \
         else if (mode == REC_FIXED) odin_launch(linear_recurrence_kernel<SL, REC_FIXED, false>, grid, dim3(threads), 0, s, p);     \
+        else if (mode == REC_GLA && blocks) odin_launch(linear_recurrence_kernel<SL, REC_GLA, true>, grid, dim3(threads), 0, s, p);  \
+        else if (mode == REC_GLA) odin_launch(linear_recurrence_kernel<SL, REC_GLA, false>, grid, dim3(threads), 0, s, p);     \
+        else if (mode == REC_SSD && blocks) odin_launch(linear_recurrence_kernel<SL, REC_SSD, true>, grid, dim3(threads), 0, s, p);  \
+        else if (mode == REC_SSD) odin_launch(linear_recurrence_kernel<SL, REC_SSD, false>, grid, dim3(threads), 0, s, p);     \
         else if (blocks) odin_launch(linear_recurrence_kernel<SL, REC_GATED, true>, grid, dim3(threads), 0, s, p);  \
         else odin_launch(linear_recurrence_kernel<SL, REC_GATED, false>, grid, dim3(threads), 0, s, p);         \
     } while (0)

@@ -531,24 +531,145 @@ extern "C" int odin_sigmoid_gate(void* o, int o_dtype, long long o_stride, const
     return 0;
 }
 
-// ------------------------------------------------------------ cap on 32-bit values, in place
-// z <- cap * tanh(z / cap)
-__global__ void __launch_bounds__(256) softcap_kernel(float* __restrict__ z, size_t stride, int rows, int n, float cap) {
+// ------------------------------------------------------------ cap and factor on 32-bit values, in place
+// z <- scale * cap * tanh(z / cap)   (cap 0: z <- scale * z)
+__global__ void __launch_bounds__(256) softcap_kernel(float* __restrict__ z, size_t stride, int rows, int n, float cap,
+                                                      float scale) {
     pdl_trigger();
     pdl_wait();
     const long long total = (long long)rows * n;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
         float* p = z + (size_t)(i / n) * stride + (i % n);
-        *p = cap * tanhf(*p / cap);
+        const float v = cap > 0.f ? cap * tanhf(*p / cap) : *p;
+        *p = scale == 1.0f ? v : v * scale;
     }
 }
 
-extern "C" int odin_softcap(float* z, long long stride, int rows, int n, float cap, void* stream) {
+extern "C" int odin_softcap(float* z, long long stride, int rows, int n, float cap, float scale, void* stream) {
     if (rows <= 0 || n <= 0) return 0;
-    if (!(cap > 0.f)) return ODIN_ERR_BAD_ARG;
+    if (cap < 0.f) return ODIN_ERR_BAD_ARG;
     const long long total = (long long)rows * n;
     const int blocks = (int)((total + 255) / 256 > 148 * 16 ? 148 * 16 : (total + 255) / 256);
-    odin_launch(softcap_kernel, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, z, (size_t)stride, rows, n, cap);
+    odin_launch(softcap_kernel, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, z, (size_t)stride, rows, n, cap, scale);
+    ODIN_LAUNCH_CHECK();
+    return 0;
+}
+
+
+// ------------------------------------------------------------ several terms into one update, normed, added, normed again
+// y = sum_i scale_i * rowscale_i[r] * f_i(sum of term i's parts), f_i the identity or w_i * v / rms(v) over the row;
+// then x[r] += post_w * y / rms(y) (post_w null: x[r] += y), and out = next_w * x[r] / rms(x[r]) (next_w null: no output).
+// Without x the sum itself goes to out as 32-bit values.  rows: gather these rows (x is then left as it is).
+// One CTA per row; every sum runs in an order that the width and the block size fix.
+#define COMBINE_MAX_TERMS 4
+struct CombineTerm {
+    const void* p; int is_bf16; int n_split; long long split_stride;
+    float scale; const float* row_scale; VecRef norm_w; float norm_eps;
+};
+struct CombineArgs { CombineTerm t[COMBINE_MAX_TERMS]; int n; };
+
+template <typename TO>
+__global__ void __launch_bounds__(ROW_THREADS)
+combine_add_kernel(float* __restrict__ x, CombineArgs a, VecRef post_w, float post_eps, VecRef next_w, float next_eps,
+                   TO* __restrict__ out, const int* __restrict__ rows, const int* __restrict__ tok_seq, int d) {
+    __shared__ float red[32];
+    extern __shared__ float cbuf[];
+    float* acc = cbuf;        // d
+    float* tmp = cbuf + d;    // d
+    pdl_trigger();
+    const int r = rows != nullptr ? rows[blockIdx.x] : blockIdx.x;
+    pdl_wait();
+    if (tok_seq != nullptr && tok_seq[r] < 0) return;
+    for (int j = threadIdx.x; j < d; j += blockDim.x) acc[j] = 0.f;
+    for (int i = 0; i < a.n; ++i) {
+        const CombineTerm& tm = a.t[i];
+        float ss = 0.f;
+        for (int j = threadIdx.x; j < d; j += blockDim.x) {
+            float v = 0.f;
+            for (int sp = 0; sp < tm.n_split; ++sp) {
+                const size_t at = (size_t)sp * tm.split_stride + (size_t)r * d + j;
+                v += tm.is_bf16 ? __bfloat162float(((const bf16*)tm.p)[at]) : ((const float*)tm.p)[at];
+            }
+            tmp[j] = v;
+            ss += v * v;
+        }
+        float f = tm.scale;
+        if (tm.row_scale != nullptr) f *= tm.row_scale[r];
+        if (tm.norm_w.p != nullptr) {
+            ss = block_sum(ss, red);
+            ss /= (float)d;
+            ss += tm.norm_eps;
+            const float rs = 1.0f / sqrtf(ss);
+            for (int j = threadIdx.x; j < d; j += blockDim.x) acc[j] += f * (tm.norm_w.at(j) * (rs * tmp[j]));
+        } else {
+            for (int j = threadIdx.x; j < d; j += blockDim.x) acc[j] += f * tmp[j];
+        }
+    }
+    if (x == nullptr) {
+        for (int j = threadIdx.x; j < d; j += blockDim.x) out[(size_t)blockIdx.x * d + j] = from_f32<TO>(acc[j]);
+        return;
+    }
+    float rs = 1.0f;
+    if (post_w.p != nullptr) {
+        float ss = 0.f;
+        for (int j = threadIdx.x; j < d; j += blockDim.x) ss += acc[j] * acc[j];
+        ss = block_sum(ss, red);
+        ss /= (float)d;
+        ss += post_eps;
+        rs = 1.0f / sqrtf(ss);
+    }
+    float* xr = x + (size_t)r * d;
+    float s2 = 0.f;
+    for (int j = threadIdx.x; j < d; j += blockDim.x) {
+        const float v = xr[j] + (post_w.p != nullptr ? post_w.at(j) * (rs * acc[j]) : acc[j]);
+        if (rows == nullptr) xr[j] = v;
+        tmp[j] = v;
+        s2 += v * v;
+    }
+    if (next_w.p == nullptr) return;
+    s2 = block_sum(s2, red);
+    s2 /= (float)d;
+    s2 += next_eps;
+    const float r2 = 1.0f / sqrtf(s2);
+    for (int j = threadIdx.x; j < d; j += blockDim.x)
+        out[(size_t)blockIdx.x * d + j] = from_f32<TO>(next_w.at(j) * (r2 * tmp[j]));
+}
+
+extern "C" int odin_combine_add(float* x, int n_terms, const void* const* ptrs, const int* dtypes, const int* n_splits,
+                                const long long* split_strides, const float* scales, const float* const* row_scales,
+                                const void* const* norm_ws, const int* norm_w_dtypes, const float* norm_eps,
+                                const void* post_w, int post_w_dtype, float post_eps, const void* next_w, int next_w_dtype,
+                                float next_eps, void* out, int out_dtype, const int* rows, const int* tok_seq, int n_rows,
+                                int d, void* stream) {
+    if (n_rows <= 0) return 0;
+    if (n_terms < 0 || n_terms > COMBINE_MAX_TERMS || d <= 0) return ODIN_ERR_BAD_ARG;
+    if (x == nullptr && (out == nullptr || out_dtype != ODIN_F32)) return ODIN_ERR_BAD_ARG;
+    if (next_w != nullptr && out == nullptr) return ODIN_ERR_BAD_ARG;
+    const size_t smem = (size_t)2 * d * sizeof(float);
+    if (smem > 200 * 1024) return ODIN_ERR_UNSUPPORTED;
+    CombineArgs a;
+    a.n = n_terms;
+    for (int i = 0; i < n_terms; ++i) {
+        if (dtypes[i] != ODIN_BF16 && dtypes[i] != ODIN_F32) return ODIN_ERR_UNSUPPORTED;
+        a.t[i].p = ptrs[i]; a.t[i].is_bf16 = dtypes[i] == ODIN_BF16; a.t[i].n_split = n_splits[i];
+        a.t[i].split_stride = split_strides[i]; a.t[i].scale = scales[i]; a.t[i].row_scale = row_scales[i];
+        a.t[i].norm_w = VecRef{norm_ws[i], norm_w_dtypes[i] == ODIN_BF16}; a.t[i].norm_eps = norm_eps[i];
+    }
+    cudaStream_t s = (cudaStream_t)stream;
+    VecRef pw{post_w, post_w_dtype == ODIN_BF16}, nw{next_w, next_w_dtype == ODIN_BF16};
+#define GO(TO)                                                                                                       \
+    do {                                                                                                             \
+        if (smem > 48 * 1024) {                                                                                      \
+            cudaError_t e = cudaFuncSetAttribute(combine_add_kernel<TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            if (e != cudaSuccess) return (int)e;                                                                     \
+        }                                                                                                            \
+        odin_launch(combine_add_kernel<TO>, dim3(n_rows), dim3(ROW_THREADS), smem, s, x, a, pw, post_eps, nw, next_eps, \
+                    (TO*)out, rows, tok_seq, d);                                                                     \
+    } while (0)
+    if (out == nullptr || out_dtype == ODIN_F32) GO(float);
+    else if (out_dtype == ODIN_BF16) GO(bf16);
+    else return ODIN_ERR_UNSUPPORTED;
+#undef GO
     ODIN_LAUNCH_CHECK();
     return 0;
 }

@@ -89,6 +89,11 @@ class DecoderModel:
                 kv = type(kv).keeping_for_all([kv] + readers)
             cache.add_entry(kv, mixer.state_bytes(), e.reads_cache_of)
             writes.append(e.reads_cache_of is None)
+        # an embedding that keeps something per sequence (the token before) gets a state entry after the layers'
+        own = getattr(self.embedding, "state_bytes", lambda: 0)()
+        if own > 0:
+            self.embedding.state_entry = cache.add_entry(None, own)
+            writes.append(False)
         cache.entry_writes = writes
 
     def forward(self, rt, step) -> torch.Tensor | None:

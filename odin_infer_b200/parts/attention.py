@@ -20,8 +20,12 @@ class GQAttention(Mixer):
     The three projection matrices are fused into one at load time.
 
     qk_norm: True: RMSNorm with the weights `q_norm` / `k_norm` before the rotation; "unit_after":
-    q and k heads divided by their root mean square after the rotation, no weight; False: none.
-    biases: names of bias vectors of the projections ({"q", "k", "v", "o"}), added in the projection.
+    q and k heads divided by their root mean square after the rotation, no weight; "whole": one RMSNorm over the
+    token's whole q projection (all heads at once, weight [n_q_heads * head_dim]) and one over its whole k projection,
+    before the rotation; False: none.
+    biases: names of bias vectors of the projections ({"q", "k", "v"} and optionally "o"), added in the projection.
+    The rotation pairs elements as its position encoding's layout says ("halves": i with i + dims/2; "pairs": 2i with
+    2i + 1).
     scale: factor on q . k (0: 1 / sqrt(head_dim)).  softcap > 0: scores become
     softcap * tanh(score / softcap) before the softmax.  v_head_dim: size of a value head (0: head_dim).
     sink: name of a tensor [n_q_heads]: a learned logit per query head whose exponential joins the softmax's
@@ -31,6 +35,7 @@ class GQAttention(Mixer):
     """
 
     graph_safe = True
+    rope_layouts = ("halves", "pairs")
 
     def __init__(self, width: int, n_q_heads: int, n_kv_heads: int, head_dim: int, names: dict,
                  position_encoding: str | None = None, qk_norm=True, eps: float = 1e-6,
@@ -39,19 +44,20 @@ class GQAttention(Mixer):
                  gate: str | None = None, gate_per_head: bool = False):
         if n_q_heads % n_kv_heads:
             raise ValueError(f"{n_q_heads} query heads are not a multiple of {n_kv_heads} kv heads")
-        if qk_norm not in (True, False, "unit_after"):
-            raise ValueError(f"qk_norm must be True, False or 'unit_after', got {qk_norm!r}")
+        if qk_norm not in (True, False, "unit_after", "whole"):
+            raise ValueError(f"qk_norm must be True, False, 'unit_after' or 'whole', got {qk_norm!r}")
         self.width, self.n_q, self.n_kv, self.hd = width, n_q_heads, n_kv_heads, head_dim
         self.vd = int(v_head_dim) or head_dim
         self.names, self.pe_name = dict(names), position_encoding
-        self.qk_norm, self.eps, self.window, self.kv_shared = qk_norm is True, float(eps), int(window), kv_shared
+        self.qk_norm, self.eps, self.window, self.kv_shared = qk_norm in (True, "whole"), float(eps), int(window), kv_shared
         self.unit_after = qk_norm == "unit_after"
+        self.whole_norm = qk_norm == "whole"
         self.chunk, self.scale, self.softcap = int(chunk), float(scale), float(softcap)
         self.bias_names = dict(biases) if biases else None
         # the heads as the first architecture has them: the fast kernels' ground
         self.sink_name, self.gate_name, self.gate_per_head = sink, gate, bool(gate_per_head)
         self.n_gate = 0 if gate is None else (self.n_q if self.gate_per_head else self.n_q * self.vd)
-        self.plain_heads = (self.bias_names is None and not self.unit_after and self.vd == self.hd
+        self.plain_heads = (self.bias_names is None and not self.unit_after and not self.whole_norm and self.vd == self.hd
                             and self.chunk == 0 and self.scale == 0.0 and self.softcap == 0.0
                             and sink is None and gate is None)
         self.sink = None
@@ -67,15 +73,16 @@ class GQAttention(Mixer):
                     ParamSpec(n["v"], (self.n_kv * self.vd, self.width))]
         out.append(ParamSpec(n["o"], (self.width, self.n_q * self.vd)))
         if self.qk_norm:
-            out.append(ParamSpec(n["q_norm"], (self.hd,), init="norm"))
+            out.append(ParamSpec(n["q_norm"], (self.n_q * self.hd if self.whole_norm else self.hd,), init="norm"))
             if not self.kv_shared:
-                out.append(ParamSpec(n["k_norm"], (self.hd,), init="norm"))
+                out.append(ParamSpec(n["k_norm"], (self.n_kv * self.hd if self.whole_norm else self.hd,), init="norm"))
         if self.bias_names is not None:
             b = self.bias_names
             out.append(ParamSpec(b["q"], (self.n_q * self.hd,)))
             if not self.kv_shared:
                 out += [ParamSpec(b["k"], (self.n_kv * self.hd,)), ParamSpec(b["v"], (self.n_kv * self.vd,))]
-            out.append(ParamSpec(b["o"], (self.width,)))
+            if b.get("o"):
+                out.append(ParamSpec(b["o"], (self.width,)))
         if self.sink_name is not None:
             out.append(ParamSpec(self.sink_name, (self.n_q,), init="logit"))
         if self.gate_name is not None:
@@ -109,7 +116,7 @@ class GQAttention(Mixer):
             if len({t.dtype for t in parts}) > 1:
                 parts = [t.float() for t in parts]
             self.b_qkv = torch.cat(parts, dim=0).contiguous()
-            self.b_o = tensors[b["o"]]
+            self.b_o = tensors[b["o"]] if b.get("o") else None
         self._dummy = torch.zeros(1, 1, dtype=torch.float32, device=rt.device)
 
     def cache_request(self):
@@ -155,13 +162,14 @@ class GQAttention(Mixer):
         cos, sin, rot_dim = rot if rot is not None else (self._dummy, self._dummy, 0)
         writes = step.writes_cache(entry) and not self.kv_shared
         o = rt.empty(T, self.n_q * self.vd)
-        if not self.plain_heads:
+        pairs = rot is not None and getattr(self.pe, "layout", "halves") == "pairs"
+        if not self.plain_heads or pairs:
             q_out = rt.empty(T, self.n_q * self.hd)
             q = ops.head_prep(qkv, self.n_q, 0 if self.kv_shared else self.n_kv, self.hd,
                               self.q_norm if self.qk_norm else None, self.k_norm if self.qk_norm else None, self.eps,
                               cos, sin, rot_dim, step.tok_pos, step.tok_seq, block_table, k_line, v_line,
                               write_kv=writes, q_out=q_out, bias=self.b_qkv, unit_norm_after=self.unit_after,
-                              v_head_dim=self.vd)
+                              v_head_dim=self.vd, whole_norm=self.whole_norm, pairs=pairs)
             rt.attention(step, q, o, self.n_q, self.n_kv, self.hd, k_line, v_line, block_table, self.window,
                          chunk=self.chunk, scale=self.scale, softcap=self.softcap, v_head_dim=self.vd, sink=self.sink)
             if self.gate_name is not None:

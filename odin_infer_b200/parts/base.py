@@ -126,6 +126,21 @@ class Scaled:
         self.update, self.factor = update, float(factor)
 
 
+class Combined(list):
+    """An update that is a sum of terms, each a tensor ([n, width] or partial sums) times a factor, optionally times a
+    number per row, optionally divided by its own root mean square and multiplied by a weight first (`ops.Term`): what a
+    mixer of two branches answers.  Only a norm that says `takes_terms` may follow."""
+
+
+class Normed:
+    """An update that passes an RMSNorm of its own before it is added: x += weight * u / rms(u), u the sum of `update`
+    (a tensor, `Several` or `Combined`).  Only a norm that says `takes_terms` may follow; it does the sum, this norm,
+    the add and its own norm in one kernel."""
+
+    def __init__(self, update, weight: torch.Tensor, eps: float):
+        self.update, self.weight, self.eps = update, weight, float(eps)
+
+
 def update_factor(pending) -> float:
     """The factor on a pending update (1 unless it is `Scaled`)."""
     return pending.factor if isinstance(pending, Scaled) else 1.0
@@ -135,6 +150,8 @@ def split_update(pending):
     """(delta, bias) of what a mixer or feed-forward answered: each a tensor or None (delta a list of
     tensors for `Several`).  The factor of a `Scaled` update is asked for with `update_factor`."""
     bias = None
+    if isinstance(pending, (Normed, Combined)):
+        return pending, None
     if isinstance(pending, Scaled):
         pending = pending.update
     if isinstance(pending, Biased):
@@ -159,6 +176,7 @@ class Norm(Part):
     takes_bias = False
     takes_several = False   # `delta` may be a list of up to three updates
     takes_scale = False     # takes a keyword `scale=`: x += scale * (the updates)
+    takes_terms = False     # `delta` may be `Combined` or `Normed`
 
 
 class PositionEncoding(Part):

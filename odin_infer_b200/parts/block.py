@@ -1,7 +1,8 @@
 """How a layer's parts are arranged."""
 from __future__ import annotations
 
-from .base import Block, PartSpec, ResidualAdded, Scaled, Several, build_part, register_part, split_update, update_factor
+from .base import (Block, Combined, Normed, PartSpec, ResidualAdded, Scaled, Several, build_part, register_part, split_update,
+                   update_factor)
 
 
 @register_part("block", "prenorm")
@@ -11,12 +12,23 @@ class PreNormBlock(Block):
 
     Each residual add is carried out by the norm that follows it: the block hands
     the update it has not yet added to whoever runs next.  A block may have no feed-forward
-    (and then no second norm)."""
+    (and then no second norm).
+
+    post_norm_mixer / post_norm_feed_forward: a plain RMSNorm on the sublayer's output before it is added,
+    x -> x + Norm_b(Mixer(Norm(x))); the update travels as `Normed` to the norm that runs next, whose kernel sums the
+    sublayer's terms, norms them, adds and norms again.  No product then adds itself to x in its epilogue."""
 
     def __init__(self, mixer: PartSpec, feed_forward: PartSpec | None, norm_mixer: PartSpec,
-                 norm_feed_forward: PartSpec | None, extras: tuple = ()):
+                 norm_feed_forward: PartSpec | None, extras: tuple = (), post_norm_mixer: PartSpec | None = None,
+                 post_norm_feed_forward: PartSpec | None = None):
         if (feed_forward is None) != (norm_feed_forward is None):
             raise ValueError("a block has a feed-forward and its norm, or neither")
+        self.post_mixer = build_part("norm", post_norm_mixer) if post_norm_mixer is not None else None
+        self.post_ffn = build_part("norm", post_norm_feed_forward) if (post_norm_feed_forward is not None
+                                                                        and feed_forward is not None) else None
+        for post in (self.post_mixer, self.post_ffn):
+            if post is not None and (getattr(post, "groups", 1) != 1 or not hasattr(post, "weight")):
+                raise TypeError("a norm on a sublayer's output is a plain RMSNorm")
         self._mixer = build_part("mixer", mixer)
         self.ffn = build_part("feed_forward", feed_forward) if feed_forward is not None else None
         self.norm_mixer = build_part("norm", norm_mixer)
@@ -28,7 +40,8 @@ class PreNormBlock(Block):
         return self._mixer
 
     def _parts(self):
-        return tuple(p for p in (self.norm_mixer, self._mixer, self.norm_ffn, self.ffn, *self.extras) if p is not None)
+        return tuple(p for p in (self.norm_mixer, self._mixer, getattr(self, "post_mixer", None), self.norm_ffn, self.ffn,
+                                 getattr(self, "post_ffn", None), *self.extras) if p is not None)
 
     def params(self):
         return [p for part in self._parts() for p in part.params()]
@@ -50,6 +63,9 @@ class PreNormBlock(Block):
     @staticmethod
     def _norm(norm, rt, x, pending, **more):
         delta, bias = split_update(pending)
+        if isinstance(delta, (Normed, Combined)):
+            if not norm.takes_terms:
+                raise TypeError(f"{type(norm).__name__} follows an update of several terms or with a norm of its own, and takes none")
         factor = update_factor(pending)
         if factor != 1.0:
             if not norm.takes_scale:
@@ -64,10 +80,16 @@ class PreNormBlock(Block):
     def forward(self, rt, step, x, pending, entry):
         mixer, ffn = self._mixer, self.ffn
         h = self._norm(self.norm_mixer, rt, x, pending)
-        pending = mixer.forward(rt, step, h, entry, residual=x) if mixer.takes_residual else mixer.forward(rt, step, h, entry)
+        if self.post_mixer is not None:
+            pending = Normed(mixer.forward(rt, step, h, entry), self.post_mixer.weight, self.post_mixer.eps)
+        else:
+            pending = mixer.forward(rt, step, h, entry, residual=x) if mixer.takes_residual else mixer.forward(rt, step, h, entry)
         if ffn is not None:
             h = self._norm(self.norm_ffn, rt, x, pending)
-            pending = ffn.forward(rt, step, h, residual=x) if ffn.takes_residual else ffn.forward(rt, step, h)
+            if self.post_ffn is not None:
+                pending = Normed(ffn.forward(rt, step, h), self.post_ffn.weight, self.post_ffn.eps)
+            else:
+                pending = ffn.forward(rt, step, h, residual=x) if ffn.takes_residual else ffn.forward(rt, step, h)
         for extra in self.extras:
             x, pending = extra.forward(rt, step, x, pending)
         if isinstance(pending, Scaled):

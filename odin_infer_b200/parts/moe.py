@@ -4,7 +4,7 @@ from __future__ import annotations
 import torch
 
 from ..csrc import ops
-from .base import FeedForward, ParamSpec, Several, register_part
+from .base import Combined, FeedForward, ParamSpec, Several, register_part
 
 
 @register_part("feed_forward", "routed_experts")
@@ -28,6 +28,11 @@ class RoutedExperts(FeedForward):
     sigmoid(z) (no bias); the experts form `groups` equal groups of neighbours, a group's score is the sum of its
     two largest scores, only experts of the `keep` best groups can be chosen, the `top` largest scores among them
     are, and their weights are the scores divided by their sum (+ 1e-20), times `route_scale`.
+    score "softmax_corrected_in_groups": scores softmax(z) over all rows of the router; the experts are chosen by score +
+    correction (the tensor names["router_bias"], which the weights do not see), a group's score is its largest choice
+    score, and the weights are the chosen scores / (their sum + 1e-20) * route_scale.
+    n_pass: the router has that many rows more than there are experts; a token that chooses one of them gets its own input
+    back, times the weight (they count as the last members of the groups; they have no tensors).
     shared_gate: the shared expert's output is multiplied by sigmoid(g . h), one number per token, g the tensor
     names["shared_token_gate"] ([1, width]); g rides as one more row of the router's matrix.
 
@@ -38,17 +43,20 @@ class RoutedExperts(FeedForward):
 
     def __init__(self, width: int, inner: int, n_experts: int, top: int, names: dict, activation: str = "silu",
                  shared_inner: int = 0, gated: bool = True, score: str = "softmax_of_chosen", groups: int = 1,
-                 keep: int = 1, route_scale: float = 1.0, shared_gate: bool = False):
-        if not (0 < top <= n_experts):
-            raise ValueError(f"every token uses {top} of {n_experts} experts: not possible")
+                 keep: int = 1, route_scale: float = 1.0, shared_gate: bool = False, n_pass: int = 0):
+        n_rows = n_experts + int(n_pass)
+        if not (0 < top <= n_rows) or n_pass < 0:
+            raise ValueError(f"every token uses {top} of {n_rows} experts: not possible")
+        if n_pass and score != "softmax_corrected_in_groups":
+            raise ValueError("rows of the router without an expert go with the score 'softmax_corrected_in_groups'")
         if activation not in (("silu", "gelu_tanh") if gated else ("silu", "gelu_tanh", "relu2")):
             raise ValueError(f"an expert's activation is silu or gelu_tanh (or relu2 without a gate), got '{activation}'")
         if score not in ops.ROUTER_SCORES:
             raise ValueError(f"a router scores by one of {', '.join(ops.ROUTER_SCORES)}, got '{score}'")
-        if groups < 1 or n_experts % groups or not (1 <= keep <= groups) or keep * (n_experts // groups) < top:
-            raise ValueError(f"{n_experts} experts in {groups} groups of which {keep} stay cannot give {top} experts a token")
-        if groups > 1 and score != "sigmoid_in_groups":
-            raise ValueError("groups of experts go with the score 'sigmoid_in_groups'")
+        if groups < 1 or n_rows % groups or not (1 <= keep <= groups) or keep * (n_rows // groups) < top:
+            raise ValueError(f"{n_rows} experts in {groups} groups of which {keep} stay cannot give {top} experts a token")
+        if groups > 1 and score == "softmax_of_chosen":
+            raise ValueError("groups of experts go with the scores 'sigmoid_in_groups' and 'softmax_corrected_in_groups'")
         if shared_gate and not shared_inner:
             raise ValueError("a gate on the shared expert needs a shared expert")
         if shared_gate and gated:
@@ -56,7 +64,7 @@ class RoutedExperts(FeedForward):
         self.width, self.inner, self.n_experts, self.top = width, inner, n_experts, top
         self.names, self.activation, self.shared_inner = dict(names), activation, int(shared_inner)
         self.gated, self.score, self.groups, self.keep = bool(gated), score, int(groups), int(keep)
-        self.route_scale, self.shared_gate = float(route_scale), bool(shared_gate)
+        self.route_scale, self.shared_gate, self.n_pass = float(route_scale), bool(shared_gate), int(n_pass)
         # the shared expert as experts of the common size that every token uses
         self.shared_as_experts = self.shared_inner // inner if (self.shared_inner and self.shared_inner % inner == 0) else 0
         self.w_router = self.b_router = self.w_gate_up = self.w_down = self.ws_gate_up = self.ws_down = None
@@ -69,9 +77,9 @@ class RoutedExperts(FeedForward):
 
     def params(self):
         n = self.names
-        out = [ParamSpec(n["router"], (self.n_experts, self.width))]
+        out = [ParamSpec(n["router"], (self.n_experts + self.n_pass, self.width))]
         if n.get("router_bias"):
-            out.append(ParamSpec(n["router_bias"], (self.n_experts,), init="near_zero"))
+            out.append(ParamSpec(n["router_bias"], (self.n_experts + self.n_pass,), init="near_zero"))
         for e in range(self.n_experts):
             *ups, d = self._expert_names(e)
             out += [ParamSpec(u, (self.inner, self.width)) for u in ups] + [ParamSpec(d, (self.width, self.inner))]
@@ -134,10 +142,19 @@ class RoutedExperts(FeedForward):
             logits = rt.linear(h, self.w_router, out_dtype=torch.float32)
         beside = self.ws_gate_up is not None   # a shared expert that runs as a dense feed-forward beside the experts
         gate = rt.empty(T, dtype=torch.float32) if (self.shared_gate and beside) else None
+        passed = rt.empty(T, dtype=torch.float32) if self.n_pass else None
         ops.moe_router(h, self.w_router, self.b_router, self.top, self.shared_as_experts, step.tok_seq, ids, wts, logits,
                        score=self.score, groups=self.groups, keep=self.keep, route_scale=self.route_scale,
-                       gate_row=self.shared_gate, gate_out=gate)
+                       gate_row=self.shared_gate, gate_out=gate, n_real=self.n_experts, pass_out=passed)
         y = rt.experts(h, self.w_gate_up, self.w_down, ids, wts, self.activation, gated=self.gated)
+        if self.n_pass:
+            # the input itself, times the summed weight of the chosen rows that have no expert, is one more term
+            terms = Combined([ops.Term(y)])
+            if beside:
+                act = rt.gated_linear(h, self.ws_gate_up, self.shared_inner, self.activation)
+                terms.append(ops.Term(rt.linear(act, self.ws_down, out_dtype=torch.float32, may_split=True)))
+            terms.append(ops.Term(h, 1.0, passed))
+            return terms
         if not beside:
             return y
         if self.gated:

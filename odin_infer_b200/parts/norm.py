@@ -4,7 +4,18 @@ from __future__ import annotations
 import torch
 
 from ..csrc import ops
-from .base import Norm, ParamSpec, register_part
+from .base import Combined, Norm, Normed, ParamSpec, Several, register_part
+
+
+def terms_of(update) -> list:
+    """The `ops.Term`s whose sum an update is."""
+    if isinstance(update, Combined):
+        return list(update)
+    if isinstance(update, Several):
+        return [ops.Term(u) for u in update if u is not None]
+    if torch.is_tensor(update):
+        return [ops.Term(update)]
+    raise TypeError(f"an update of type {type(update).__name__} cannot be summed term by term")
 
 
 @register_part("norm", "rmsnorm")
@@ -20,6 +31,7 @@ class RMSNorm(Norm):
     takes_bias = True
     takes_several = True
     takes_scale = True
+    takes_terms = True
 
     def __init__(self, width: int, eps: float, weight: str, groups: int = 1, one_plus: bool = False):
         if groups < 1 or width % groups:
@@ -49,6 +61,13 @@ class RMSNorm(Norm):
         """second: a norm that `pairs_with` this one; both outputs of the one updated row come back, (out, out2)."""
         n = x.shape[0] if rows is None else rows.numel()
         out = rt.empty(n, self.width)
+        if isinstance(delta, (Normed, Combined)):
+            # a sum of terms, a norm of the update's own, the add and this norm: one kernel
+            if self.groups != 1 or bias is not None or scale != 1.0 or second is not None:
+                raise TypeError("an update of several terms or with a norm of its own meets a plain RMSNorm only")
+            post_w, post_eps, inner = (delta.weight, delta.eps, delta.update) if isinstance(delta, Normed) else (None, 0.0, delta)
+            ops.combine_add(x, terms_of(inner), post_w, post_eps, self.weight, self.eps, out, rows)
+            return out
         if isinstance(delta, (list, tuple)) and len(delta) == 1:
             delta = delta[0]
         if delta is None and bias is None:

@@ -226,3 +226,69 @@ class GatedLinearRecurrence(Mixer):
         y = rt.empty(T, vv)
         ops.head_unit_scale(o, self.norm_w, False, None, self.eps, y, self.H, self.V)
         return rt.linear(y, self.w_o, out_dtype=torch.float32, may_split=True, add_to=residual)
+
+
+@register_part("mixer", "gated_linear_attention")
+class GatedLinearAttention(Mixer):
+    """Linear attention whose state decays per key channel by a gate of the input.
+
+    q = W_q h * head_dim^(-1/2), k = W_k h (heads x head_dim), v = W_v h (heads x v_head_dim); the decay per head and key
+    channel is a = sigmoid(W_a2 (W_a1 h) + b_a2)^(1 / tau), formed as exp(logsigmoid(.) / tau).  Per head:
+
+        S_t = diag(a_t) S_(t-1) + k_t v_t^T          o_t = S_t^T q_t
+
+    Each head's o goes through an RMSNorm over v_head_dim with one weight shared by the heads; the heads, side by side,
+    are multiplied by silu(W_g h) and go through W_o.  q, k, v and g are one product that leaves its sums as 32-bit; the
+    inner size of the decay's two-step projection is taken from the tensors of a model folder (random weights need it
+    given).  names: "q", "k", "v", "g", "o", "norm", "a1", "a2", "a2_bias"."""
+
+    graph_safe = True
+
+    def __init__(self, width: int, n_heads: int, head_dim: int, v_head_dim: int, tau: float, names: dict, eps: float = 1e-5,
+                 decay_rank: int = 0):
+        if not tau > 0:
+            raise ValueError(f"tau must be positive, got {tau}")
+        self.width, self.H, self.D, self.V, self.eps = width, n_heads, head_dim, v_head_dim, float(eps)
+        self.tau, self.names, self.rank = float(tau), dict(names), int(decay_rank)
+
+    def params(self):
+        n, qk, vv = self.names, self.H * self.D, self.H * self.V
+        rank = self.rank or -1
+        fill = self.rank or 16
+        return [ParamSpec(n["q"], (qk, self.width)), ParamSpec(n["k"], (qk, self.width)),
+                ParamSpec(n["v"], (vv, self.width)), ParamSpec(n["g"], (vv, self.width)),
+                ParamSpec(n["o"], (self.width, vv)), ParamSpec(n["norm"], (self.V,), init="norm"),
+                ParamSpec(n["a1"], (rank, self.width), shape_if_random=(fill, self.width)),
+                ParamSpec(n["a2"], (qk, rank), shape_if_random=(qk, fill)),
+                ParamSpec(n["a2_bias"], (qk,), init="logit")]
+
+    def bind(self, tensors, rt):
+        n = self.names
+        mats = [tensors.pop(n[s]) for s in ("q", "k", "v", "g")]
+        if len({t.dtype for t in mats}) > 1:
+            mats = [t.float() for t in mats]
+        self.w_qkvg = torch.cat(mats, dim=0).contiguous()
+        self.w_a1, self.w_a2, self.w_o, self.norm_w = tensors[n["a1"]], tensors[n["a2"]], tensors[n["o"]], tensors[n["norm"]]
+        self.a_bias = tensors[n["a2_bias"]].to(torch.float32).contiguous()
+        # 1 / tau per key channel, rounded to 32-bit once
+        self.inv_tau = torch.full((self.H * self.D,), 1.0 / self.tau, dtype=torch.float64).to(torch.float32).to(rt.device)
+
+    def state_bytes(self) -> int:
+        return 4 * self.H * self.D * self.V
+
+    def kernel_groups(self):
+        return {"recurrent", "gemm_plain"}
+
+    def forward(self, rt, step, h, entry):
+        T, qk, vv = h.shape[0], self.H * self.D, self.H * self.V
+        qkvg = rt.linear(h, self.w_qkvg, out_dtype=torch.float32)
+        low = rt.linear(h, self.w_a1)
+        raw = rt.linear(low, self.w_a2, out_dtype=torch.float32)
+        o = rt.empty(T, vv, dtype=torch.float32)
+        ops.linear_recurrence("gla", qkvg[:, :qk], qkvg[:, qk:2 * qk], raw, qkvg[:, 2 * qk:2 * qk + vv], self.a_bias,
+                              self.inv_tau, o, _f32_view(step.state(entry)), step.seq_start, step.seq_slots, step.n_seq_cap,
+                              self.H, self.D, self.V, block_len=_block_len(step), max_new=step.max_new,
+                              q_scale=float(self.D) ** -0.5)
+        y = rt.empty(T, vv)
+        ops.head_unit_scale(o, self.norm_w, False, qkvg[:, 2 * qk + vv:], self.eps, y, self.H, self.V)
+        return rt.linear(y, self.w_o, out_dtype=torch.float32, may_split=True)
