@@ -911,6 +911,239 @@ def nikonex_workload(steps: int, warmup: int) -> int:
     return 0
 
 
+# --------------------------------------------------------------------------------------------------------------
+# --workload meropel: the Meropel design beside the Nikonex design (the closest: recurrences, attention, experts in groups)
+# --------------------------------------------------------------------------------------------------------------
+MEROPEL_SIZES = {
+    # the Nikonex sizes' width, layers, vocabulary and experts; attention of 16 query heads on 8 kv heads of 128 (the
+    # tensor-core kernels' head size), a selective scan of twice the width with 16 states per channel, a recurrence over
+    # heads of 128 states x 64 (twice the width in all), gated linear attention with keys of half and values of the width
+    "2048": dict(NIKONEX_SIZES["2048"], scan_inner=4096, scan_state=16, dt_rank=128, ssd_heads=64, ssd_dim=64, ssd_state=128,
+                 ssd_groups=8, gla_heads=8, gla_dim=128, gla_v=256, identity=4),
+    "4096": dict(NIKONEX_SIZES["4096"], scan_inner=8192, scan_state=16, dt_rank=256, ssd_heads=128, ssd_dim=64, ssd_state=128,
+                 ssd_groups=8, gla_heads=16, gla_dim=128, gla_v=256, identity=8),
+}
+
+
+def meropel_config(z: dict) -> dict:
+    att = {"heads": z["heads"], "kv_heads": z["kv"], "dim": z["hd"], "vdim": z["hd"], "scale": z["hd"] ** -0.5}
+    par = {"left": dict(att, rot={"dims": z["hd"] // 2, "base": 10000.0}), "left_scale": 0.8, "right_scale": 0.5,
+           "right": {"inner": z["scan_inner"], "state": z["scan_state"], "dt_rank": z["dt_rank"], "conv": 4}}
+    par2 = {"left": dict(att, rot={"dims": z["hd"], "base": 1000000.0}),
+            "right": {"heads": z["ssd_heads"], "vdim": z["ssd_dim"], "state": z["ssd_state"], "groups": z["ssd_groups"],
+                      "norm_groups": z["ssd_groups"], "conv": 4}}
+    gla = {"heads": z["gla_heads"], "dim": z["gla_dim"], "vdim": z["gla_v"], "tau": 16.0}
+    moe = {"kind": "moe", "expert": {"ff": z["eff"]}, "shared": {"ff": z["shared"]},
+           "router": {"experts": z["experts"], "identity": z["identity"], "top": z["top"], "scale": 2.5,
+                      "groups": {"count": z["groups"], "keep": z["keep"]}}}
+    kinds = [("parallel", par), ("parallel_2", par2), ("gla", gla)]
+    layers = [{"type": kinds[i % 3][0], "mixer": kinds[i % 3][1], "mlp": moe} for i in range(z["layers"])]
+    return {"architecture": "Meropel", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6}, "logit_scale": 0.25,
+            "embedding": {"bigram": {"buckets": 99991, "mul_prev": 127, "mul_cur": 7}}, "layers": layers}
+
+
+def meropel_kernels(z: dict, T: int, peaks: dict) -> dict:
+    """Every kernel that the design adds (or runs with options of its own), alone at this size for T token rows (one
+    prompt of T tokens, or T sequences of one token after 512), beside the like kernel of the closest existing path:
+    microseconds, and algorithmic bytes (or FLOPs) over the time as a fraction of the measured peaks."""
+    import torch
+    from odin_infer_b200.csrc import ops
+    from odin_infer_b200.engine import runtime as R
+    dev, bf = "cuda:0", torch.bfloat16
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    d, E, top, eff, ident = z["width"], z["experts"], z["top"], z["eff"], z["identity"]
+    always = z["shared"] // eff
+    decode = T <= 64
+    out = {}
+
+    def replayed(fn, flush, reps=5, inner=20):
+        fn()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for _ in range(inner):
+                fn()
+        return _timed(graph.replay, flush, reps) / inner
+    timed = replayed if decode else _timed
+
+    def note(name, us, nbytes=None, flops=None, **more):
+        rec = {"us": round(us, 2)}
+        if nbytes is not None:
+            rec["of_hbm"] = round(nbytes / (us * 1e-6) / 1e9 / peaks["hbm_gbs"], 3)
+        if flops is not None:
+            rec["tflops"] = round(flops / (us * 1e-6) / 1e12, 2)
+        rec.update(more)
+        out[name] = rec
+    rt = R.Runtime(dev, bf)
+    torch.manual_seed(0)
+    ctx = 512 if decode else 0
+    n_seq = T if decode else 1
+    per_seq = (ctx + 1 + 63) // 64 if decode else (T + 63) // 64
+    n_pages = n_seq * per_seq
+    bt = torch.arange(n_pages, dtype=torch.int32, device=dev).reshape(n_seq, per_seq).contiguous()
+    pos = torch.full((T,), ctx, dtype=torch.int32, device=dev) if decode else torch.arange(T, dtype=torch.int32, device=dev)
+    seq = torch.arange(T, dtype=torch.int32, device=dev) if decode else torch.zeros(T, dtype=torch.int32, device=dev)
+    starts = torch.arange(0, T + 1, 1 if decode else T, dtype=torch.int32, device=dev)
+    slots = torch.arange(n_seq, dtype=torch.int32, device=dev)
+    h = torch.randn(T, d, device=dev).to(bf)
+    x = torch.randn(T, d, device=dev)
+    w1, w2 = torch.randn(d, device=dev).to(bf), torch.randn(d, device=dev).to(bf)
+    hb = torch.empty(T, d, dtype=bf, device=dev)
+    # the residual stream: two terms, the update's own norm, the add, the next norm, beside the add of two updates and a norm
+    d1, d2 = torch.randn(T, d, device=dev), torch.randn(T, d, device=dev)
+    nb = T * d * (4 * 4 + 2)
+    note("add + RMSNorm of two updates (nikonex)", timed(lambda: ops.row_update(x, [d1, d2], None, w1, 1e-6, 1, hb), flush), nbytes=nb)
+    note("two terms with factors, their norm, the add, the next norm", timed(
+        lambda: ops.combine_add(x, [ops.Term(d1, 0.8), ops.Term(d2, 0.5)], w2, 1e-6, w1, 1e-6, hb), flush), nbytes=nb)
+    note("two terms each with a norm of its own, their norm, the add, the next norm", timed(
+        lambda: ops.combine_add(x, [ops.Term(d1, 0.5, None, w1, 1e-6), ops.Term(d2, 0.5, None, w2, 1e-6)], w2, 1e-6, w1, 1e-6, hb), flush), nbytes=nb)
+    # the embedding: a row of the token table, beside that plus a row of the pair table and the token before
+    V, buckets = z["vocab"], 99991
+    table, pairs = torch.randn(V, d, device=dev).to(bf), torch.randn(buckets + 1, d, device=dev).to(bf)
+    tok = torch.randint(0, V, (T,), dtype=torch.int32, device=dev)
+    before = torch.zeros(n_seq, 64, dtype=torch.int32, device=dev)
+    note("embedding (nikonex)", timed(lambda: ops.embed(table, tok, x), flush), nbytes=T * d * 6)
+    note("embedding plus the row of the pair (token before, token), two launches", timed(
+        lambda: ops.embed_pair(table, pairs, tok, seq, starts, slots, before, n_seq, buckets, 127, 7, x), flush), nbytes=T * d * 8)
+    # head preparation: biases, the norm over the whole projection, rotation in pairs, beside the per-head norm
+    Hq, Hkv, hd = z["heads"], z["kv"], z["hd"]
+    kc = (torch.randn(n_pages, Hkv, 64, hd, device=dev) * 0.3).to(bf)
+    vc = (torch.randn(n_pages, Hkv, 64, hd, device=dev) * 0.3).to(bf)
+    qkv = torch.randn(T, (Hq + 2 * Hkv) * hd, device=dev).to(bf)
+    bias = torch.randn((Hq + 2 * Hkv) * hd, device=dev).to(bf)
+    hn, qn, kn = torch.ones(hd, dtype=bf, device=dev), torch.ones(Hq * hd, dtype=bf, device=dev), torch.ones(Hkv * hd, dtype=bf, device=dev)
+    ch = torch.randn(max(T, ctx + 1), hd // 2, device=dev)
+    q_out = torch.empty(T, Hq * hd, dtype=bf, device=dev)
+    hb_ = T * (Hq + 2 * Hkv) * hd * 4
+    note("head preparation with a norm per head (nikonex's neighbour nufupel)", timed(
+        lambda: ops.head_prep(qkv, Hq, Hkv, hd, hn, hn, 1e-6, ch, ch, hd, pos, seq, bt, kc, vc, q_out=q_out), flush), nbytes=hb_)
+    note("head preparation with biases and a unit norm after the rotation (tovalix)", timed(
+        lambda: ops.head_prep(qkv, Hq, Hkv, hd, None, None, 1e-6, ch, ch, hd, pos, seq, bt, kc, vc, q_out=q_out, bias=bias, unit_norm_after=True), flush), nbytes=hb_)
+    note("head preparation with biases, the norm over the whole projection, rotation in pairs", timed(
+        lambda: ops.head_prep(qkv, Hq, Hkv, hd, qn, kn, 1e-6, ch, ch, hd, pos, seq, bt, kc, vc, q_out=q_out, bias=bias, whole_norm=True, pairs=True), flush), nbytes=hb_)
+    # the causal convolution with its memory
+    C, taps = z["scan_inner"], 4
+    xz = torch.randn(T, 2 * C, device=dev).to(bf)
+    cw, cb = torch.randn(C, taps, device=dev).to(bf), torch.randn(C, device=dev).to(bf)
+    cstate = torch.zeros(n_seq, (taps - 1) * C, device=dev)
+    xc = torch.empty(T, C, dtype=bf, device=dev)
+    note(f"causal convolution of {taps} taps over {C} channels with SiLU, and its memory (two launches)", timed(
+        lambda: ops.causal_conv(xz[:, :C], cw, cb, True, cstate, seq, starts, slots, n_seq, xc), flush),
+        nbytes=T * C * 4 + 2 * n_seq * (taps - 1) * C * 4)
+    # the recurrences: retention's (nikonex) beside the three of this design, decoding and a prompt
+    RH, dk, dv = z["ret_heads"], z["ret_dim"], z["ret_v"]
+    blocks = dict(block_len=128, max_new=T) if not decode else {}
+    tag = " in blocks of 128 tokens" if not decode else ""
+
+    def rec_bytes(H_, dk_, dv_, qk_cols):
+        nbytes = 4 * (T * (qk_cols + 2 * H_ * dv_) + 2 * n_seq * H_ * dk_ * dv_)
+        if not decode:
+            nbytes += 4 * (2 * T * H_ * dk_ + 3 * (T // 128) * H_ * dk_ * dv_)
+        return nbytes
+    state = torch.zeros(n_seq, RH * dk * dv, device=dev)
+    qkvg = torch.randn(T, RH * (2 * dk + 2 * dv), device=dev)
+    rq, rk, rv = qkvg[:, :RH * dk], qkvg[:, RH * dk:2 * RH * dk], qkvg[:, 2 * RH * dk:2 * RH * dk + RH * dv]
+    ro = torch.empty(T, RH * dv, device=dev)
+    decay = torch.full((RH,), 0.99, device=dev)
+    note(f"recurrence with a fixed decay ({RH} heads of {dk} x {dv}; nikonex)" + tag, timed(
+        lambda: ops.linear_recurrence("fixed", rq, rk, None, rv, decay, decay, ro, state, starts, slots, n_seq, RH, dk, dv, **blocks), flush),
+        nbytes=rec_bytes(RH, dk, dv, 2 * RH * dk))
+    GH, gk, gv = z["gla_heads"], z["gla_dim"], z["gla_v"]
+    gstate = torch.zeros(n_seq, GH * gk * gv, device=dev)
+    gq, gkk, graw = (torch.randn(T, GH * gk, device=dev) for _ in range(3))
+    gvv, go = torch.randn(T, GH * gv, device=dev), torch.empty(T, GH * gv, device=dev)
+    gb, gt = torch.randn(GH * gk, device=dev) + 2, torch.full((GH * gk,), 1 / 16.0, device=dev)
+    note(f"gated linear attention's recurrence ({GH} heads of {gk} x {gv})" + tag, timed(
+        lambda: ops.linear_recurrence("gla", gq, gkk, graw, gvv, gb, gt, go, gstate, starts, slots, n_seq, GH, gk, gv, q_scale=gk ** -0.5, **blocks), flush),
+        nbytes=rec_bytes(GH, gk, gv, 3 * GH * gk))
+    SH, sp, sn, sg = z["ssd_heads"], z["ssd_dim"], z["ssd_state"], z["ssd_groups"]
+    sstate = torch.zeros(n_seq, SH * sn * sp, device=dev)
+    xbc = torch.randn(T, SH * sp + 2 * sg * sn, device=dev)
+    sx, sB, sC = xbc[:, :SH * sp], xbc[:, SH * sp:SH * sp + sg * sn], xbc[:, SH * sp + sg * sn:]
+    sdt, so = torch.randn(T, SH, device=dev), torch.empty(T, SH * sp, device=dev)
+    sa, sbias = torch.randn(SH, device=dev) * 0.5, torch.randn(SH, device=dev) - 2
+    note(f"state-space recurrence over heads ({SH} heads of {sn} x {sp}, {sg} groups)" + tag, timed(
+        lambda: ops.linear_recurrence("ssd", sC, sB, sdt, sx, sa, sbias, so, sstate, starts, slots, n_seq, SH, sn, sp, heads_per_group=SH // sg, **blocks), flush),
+        nbytes=rec_bytes(SH, sn, sp, 2 * sg * sn))
+    inner, N = z["scan_inner"], z["scan_state"]
+    cst = torch.zeros(n_seq, inner * N, device=dev)
+    dt = torch.randn(T, inner, device=dev)
+    bc = torch.randn(T, 2 * N, device=dev)
+    a_log, dd, dtb = torch.randn(inner, N, device=dev) * 0.5, torch.randn(inner, device=dev), torch.randn(inner, device=dev) - 2
+    yb = torch.empty(T, inner, dtype=bf, device=dev)
+    note(f"selective scan ({inner} channels of {N} states) with skip and gate", timed(
+        lambda: ops.selective_scan(xc, dt, dtb, bc[:, :N], bc[:, N:], a_log, dd, xz[:, C:], cst, yb, starts, slots, n_seq), flush),
+        nbytes=T * inner * (2 + 4 + 2 + 2) + T * 2 * N * 4 + 2 * n_seq * inner * N * 4 + inner * N * 4,
+        flops=T * inner * N * 4.0)
+    # what follows a recurrence: the heads' norm with a weight and a gate, beside skip, gate and a norm in groups
+    y = torch.empty(T, RH * dv, dtype=bf, device=dev)
+    rg = qkvg[:, 2 * RH * dk + RH * dv:]
+    note("heads' unit norm times silu(gate) (nikonex)", timed(lambda: ops.head_unit_scale(ro, None, False, rg, 1e-5, y, RH, dv), flush), nbytes=T * RH * dv * 10)
+    wv = torch.ones(gv, dtype=bf, device=dev)
+    gg, gy = torch.randn(T, GH * gv, device=dev), torch.empty(T, GH * gv, dtype=bf, device=dev)
+    note("heads' norm with a shared weight times silu(gate)", timed(lambda: ops.head_unit_scale(go, wv, False, gg, 1e-5, gy, GH, gv), flush), nbytes=T * GH * gv * 10)
+    sz, sw, sy = torch.randn(T, SH * sp, device=dev), torch.ones(SH * sp, device=dev), torch.empty(T, SH * sp, dtype=bf, device=dev)
+    note("skip, silu(gate) and a norm in groups", timed(lambda: ops.skip_gate_norm(so, sx, sa, sp, sz, sw, sg, 1e-5, sy), flush), nbytes=T * SH * sp * 14)
+    # router: sigmoid scores in groups (nikonex) beside corrected softmax scores in groups with pass-through rows
+    rows_r = E + ident
+    wr = (torch.randn(rows_r + 1, d, device=dev) / d ** 0.5).to(bf)
+    ids = torch.empty(T, top + always, dtype=torch.int32, device=dev)
+    wts = torch.empty(T, top + always, dtype=torch.float32, device=dev)
+    passed = torch.empty(T, dtype=torch.float32, device=dev)
+    corr = torch.randn(rows_r, device=dev) * 0.01
+
+    def route(score, w, **kw):
+        lg = rt.linear(h, w, out_dtype=torch.float32) if T > 64 else None
+        ops.moe_router(h, w, kw.pop("bias", None), top, always, seq, ids, wts, lg, score=score, **kw)
+    rb = T * d * 2 + E * d * 2
+    note("router, sigmoid scores in groups, the shared expert's gate (nikonex)", timed(
+        lambda: route("sigmoid_in_groups", wr[:E + 1], groups=z["groups"], keep=z["keep"], route_scale=2.5, gate_row=True), flush), nbytes=rb)
+    note("router, corrected softmax scores in groups, rows that hand the input through", timed(
+        lambda: route("softmax_corrected_in_groups", wr[:rows_r], bias=corr, groups=z["groups"], keep=z["keep"], route_scale=2.5,
+                      n_real=E, pass_out=passed), flush), nbytes=rb)
+    torch.cuda.synchronize()
+    return out
+
+
+def meropel_workload(steps: int, warmup: int) -> int:
+    """The Meropel design at two sizes that resemble a real model's layers, beside the Nikonex design of the same
+    width, layers, vocabulary and experts (random weights): a prompt of 2,048 tokens in one step, decoding at batch 8
+    after 512-token prompts (device-timed), and every kernel of the design alone beside its like."""
+    import torch
+    from odin_infer_b200 import Engine, Engine_Opts
+    from odin_infer_b200.config import config_from_dict
+    from odin_infer_b200.csrc import ops
+    peaks, peak_source = load_peaks()
+    result = {"metric": "Meropel beside Nikonex at equal sizes: prompt of 2,048 tokens, decode at batch 8 (512-token prompts), "
+                        "bf16, random weights", "peak_source": peak_source, "sizes": {}}
+    steps = min(steps, 64)
+    for name, z in MEROPEL_SIZES.items():
+        entry = {}
+        for model, raw in (("meropel", meropel_config(z)), ("nikonex", nikonex_config(z))):
+            need = PROMPT + warmup + steps + 72
+            engine = Engine.random(config_from_dict(raw), WEIGHT_SEED, Engine_Opts(
+                max_ctx=CONTEXT, max_tokens=max(8 * ((need + 63) // 64 * 64), PREFILL_TOKENS + 64), max_batch=8,
+                dtype="bfloat16", verbose=False))
+            ms_pf = run_prefill(engine, z["vocab"])
+            tps, ms_step, _, launches = run_decode(engine, 8, steps, warmup, z["vocab"])
+            entry[model] = {"layers": z["layers"], "weights_gib": round(engine.weight_bytes / 2 ** 30, 2),
+                            "prefill_2048": {"ms": round(ms_pf, 3), "tokens_per_s": round(PREFILL_TOKENS / ms_pf * 1e3)},
+                            "decode_b8": {"ms_per_step": round(ms_step, 4), "tokens_per_s": round(tps, 1),
+                                          "launches_per_step": launches // steps}}
+            engine.destroy()
+            del engine
+            torch.cuda.empty_cache()
+        entry["kernels_prompt_2048_rows"] = meropel_kernels(z, PREFILL_TOKENS, peaks)
+        entry["kernels_decode_8_rows"] = meropel_kernels(z, 8, peaks)
+        result["sizes"][name] = entry
+    ops.gemm_tc_check()
+    ops.attention_prefill_check()
+    ops.attention_decode_check()
+    ops.moe_tc_check()
+    print(json.dumps(result))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -922,13 +1155,13 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
     ap.add_argument("--no-graphs", action="store_true", help="launch the decode step's kernels one by one (for profilers)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end run (for profilers)")
-    ap.add_argument("--workload", default="8b", choices=["8b", "1.7b-mixed", "32b-long", "tovalix", "nufupel", "nikonex"],
+    ap.add_argument("--workload", default="8b", choices=["8b", "1.7b-mixed", "32b-long", "tovalix", "nufupel", "nikonex", "meropel"],
                     help="8b: the contract's run (default).  The others are further workloads of the baseline's list and "
                          "print a line of their own: 1.7b-mixed = Qwen3-1.7B shape, 64 prompts of 16..2048 tokens, 128 new "
                          "tokens each; 32b-long = Qwen3-32B shape, a 2,048-token prompt, decoding 1 and 8 sequences at context 8192; "
                          "tovalix = the Tovalix design beside the Qwen3 decoder at equal sizes, and its kernels alone; "
                          "nufupel = the same for the Nufupel design; nikonex = the Nikonex design beside Nufupel at equal sizes, "
-                         "and its kernels alone")
+                         "and its kernels alone; meropel = the Meropel design beside Nikonex at equal sizes, and its kernels alone")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -946,6 +1179,8 @@ def main() -> int:
         return nufupel_workload(args.steps, warmup)
     if args.workload == "nikonex":
         return nikonex_workload(args.steps, warmup)
+    if args.workload == "meropel":
+        return meropel_workload(args.steps, warmup)
     if args.workload != "8b":
         return other_workload(args.workload)
 
