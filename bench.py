@@ -1071,8 +1071,8 @@ def meropel_kernels(z: dict, T: int, peaks: dict) -> dict:
     bc = torch.randn(T, 2 * N, device=dev)
     a_log, dd, dtb = torch.randn(inner, N, device=dev) * 0.5, torch.randn(inner, device=dev), torch.randn(inner, device=dev) - 2
     yb = torch.empty(T, inner, dtype=bf, device=dev)
-    note(f"selective scan ({inner} channels of {N} states) with skip and gate", timed(
-        lambda: ops.selective_scan(xc, dt, dtb, bc[:, :N], bc[:, N:], a_log, dd, xz[:, C:], cst, yb, starts, slots, n_seq), flush),
+    note(f"selective scan ({inner} channels of {N} states) with skip and gate" + tag, timed(
+        lambda: ops.selective_scan(xc, dt, dtb, bc[:, :N], bc[:, N:], a_log, dd, xz[:, C:], cst, yb, starts, slots, n_seq, **blocks), flush),
         nbytes=T * inner * (2 + 4 + 2 + 2) + T * 2 * N * 4 + 2 * n_seq * inner * N * 4 + inner * N * 4,
         flops=T * inner * N * 4.0)
     # what follows a recurrence: the heads' norm with a weight and a gate, beside skip, gate and a norm in groups

@@ -32,15 +32,35 @@ head_prep_kernel(const TI* qkv, int n_split, size_t split_stride, T* q_out,  // 
                  const int* __restrict__ block_table, int bt_stride, T* __restrict__ k_cache,
                  T* __restrict__ v_cache, int page_size, int write_kv, int pairs) {
     __shared__ float buf[HP_WARPS][HP_MAX_HD];
+    __shared__ float whole_ss[2][HP_WARPS];
     pdl_trigger();
     pdl_wait();
     const int t = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int head = blockIdx.y * HP_WARPS + warp;
     const int n_heads = Hq + 2 * Hkv;
-    if (head >= n_heads) return;
     const int seq = tok_seq[t];
-    if (seq < 0) return;  // padding token
+    if (seq < 0) return;  // padding token (the whole CTA: it belongs to one token)
+    if (norm_mode == 3) {
+        // the sums of squares of the token's whole q and whole k projection, by the CTA's warps together and in an order
+        // that the sizes alone fix (every CTA of the token forms the same two sums)
+        for (int side = 0; side < 2; ++side) {
+            const int whole = (side == 0 ? Hq : Hkv) * hd;
+            const size_t wcol0 = side == 0 ? 0 : (size_t)Hq * hd;
+            const TI* wsrc = qkv + (size_t)t * row_stride + wcol0;
+            float sw = 0.f;
+            for (int j = threadIdx.x; j < whole; j += HP_WARPS * 32) {
+                float v = to_f32(wsrc[j]);
+                for (int sp = 1; sp < n_split; ++sp) v += to_f32(wsrc[(size_t)sp * split_stride + j]);
+                if (bias.p != nullptr) v += bias.at((int)wcol0 + j);
+                sw += v * v;
+            }
+            sw = warp_sum(sw);
+            if (lane == 0) whole_ss[side][warp] = sw;
+        }
+        __syncthreads();
+    }
+    if (head >= n_heads) return;
     const int pos = tok_pos[t];
 
     const bool is_q = head < Hq;
@@ -81,19 +101,10 @@ head_prep_kernel(const TI* qkv, int n_split, size_t split_stride, T* q_out,  // 
         const VecRef& w = is_q ? qw : kw;
         for (int j = lane; j < hd; j += 32) b[j] = w.at(j) * (r * b[j]);
     } else if (norm_mode == 3) {
-        // the sum of squares of the whole projection of this token, in an order that its size alone fixes (every warp of
-        // the token's q heads, or k heads, forms the same sum)
         const int whole = (is_q ? Hq : Hkv) * hd;
-        const size_t wcol0 = is_q ? 0 : (size_t)Hq * hd;
-        const TI* wsrc = qkv + (size_t)t * row_stride + wcol0;
         float sw = 0.f;
-        for (int j = lane; j < whole; j += 32) {
-            float v = to_f32(wsrc[j]);
-            for (int sp = 1; sp < n_split; ++sp) v += to_f32(wsrc[(size_t)sp * split_stride + j]);
-            if (bias.p != nullptr) v += bias.at((int)wcol0 + j);
-            sw += v * v;
-        }
-        sw = warp_sum(sw);
+#pragma unroll
+        for (int wi = 0; wi < HP_WARPS; ++wi) sw += whole_ss[is_q ? 0 : 1][wi];
         sw /= (float)whole;
         sw += eps;
         const float r = 1.0f / sqrtf(sw);

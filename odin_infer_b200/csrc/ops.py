@@ -605,11 +605,16 @@ def causal_conv(src: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | No
 
 def selective_scan(x: torch.Tensor, dt: torch.Tensor, dt_bias: torch.Tensor | None, B: torch.Tensor, C: torch.Tensor,
                    A_log: torch.Tensor, D: torch.Tensor | None, z: torch.Tensor | None, state: torch.Tensor,
-                   out: torch.Tensor, seq_start: torch.Tensor, seq_slots: torch.Tensor, n_seqs: int) -> None:
+                   out: torch.Tensor, seq_start: torch.Tensor, seq_slots: torch.Tensor, n_seqs: int,
+                   block_len: int = 0, max_new: int = 0) -> None:
     """Per channel c and state index n, over each sequence's rows in order: step = softplus(dt + dt_bias),
     S[c, n] = exp(step_c A[c, n]) S[c, n] + step_c x_c B_n with A = -exp(A_log); out_c = (sum_n S[c, n] C_n + D_c x_c) *
     silu(z_c).  x, z: [T, inner] in one element type (views are fine); dt float32 [T, inner]; B, C float32 [T, N] views of
-    one row stride; state float32 [slots, >= inner N], any row stride.  Everything inside is 32-bit."""
+    one row stride; state float32 [slots, >= inner N], any row stride.  Everything inside is 32-bit.
+
+    block_len > 0 (with max_new, the most rows any sequence brings): every sequence's rows are cut into blocks of block_len
+    tokens that are walked side by side from a state of zeros; a second kernel carries the state from block to block, a
+    third adds each block's incoming state to its tokens' outputs.  The same values up to rounding; for long prompts."""
     T, inner = out.shape
     N = A_log.shape[1]
     assert tuple(x.shape) == (T, inner) and x.stride(1) == 1 and dt.dtype == torch.float32 and dt.stride(1) == 1
@@ -620,12 +625,22 @@ def selective_scan(x: torch.Tensor, dt: torch.Tensor, dt_bias: torch.Tensor | No
     assert len({w.dtype for w in ws}) == 1 and all(w.is_contiguous() for w in ws)
     if z is not None:
         assert z.dtype == x.dtype and z.stride(1) == 1 and tuple(z.shape) == (T, inner)
+    n_blocks, ytmp, cumdt, s_loc, dtot, kernels = 0, None, None, None, None, 1
+    if block_len > 0:
+        assert max_new > 0
+        n_blocks = (max_new + block_len - 1) // block_len
+        ytmp = torch.empty(T, inner, dtype=torch.float32, device=out.device)
+        cumdt = torch.empty(T, inner, dtype=torch.float32, device=out.device)
+        s_loc = torch.empty(n_seqs * n_blocks, inner * N, dtype=torch.float32, device=out.device)
+        dtot = torch.empty(n_seqs * n_blocks, inner, dtype=torch.float32, device=out.device)
+        kernels = 3
     _check(_fn("state_space", "odin_selective_scan")(
         _ptr(x), c_int(dtype_code(x.dtype)), c_longlong(x.stride(0)), _ptr(dt), c_longlong(dt.stride(0)), _ptr(dt_bias),
         _ptr(B), _ptr(C), c_longlong(B.stride(0)), _ptr(A_log), _ptr(D), c_int(dtype_code(A_log.dtype)), _ptr(z),
         c_longlong(z.stride(0) if z is not None else 0), _ptr(state), c_longlong(state.stride(0)), _ptr(out),
         c_int(dtype_code(out.dtype)), c_longlong(out.stride(0)), _ptr(seq_start), _ptr(seq_slots), c_int(n_seqs),
-        c_int(inner), c_int(N), _stream()), "selective_scan")
+        c_int(inner), c_int(N), c_int(block_len), c_int(n_blocks), _ptr(ytmp), _ptr(cumdt), _ptr(s_loc), _ptr(dtot),
+        _stream()), "selective_scan", kernels=kernels)
 
 
 def skip_gate_norm(o: torch.Tensor, x: torch.Tensor | None, D: torch.Tensor | None, head_dim: int, z: torch.Tensor | None,

@@ -130,7 +130,8 @@ linear_recurrence_kernel(RecParams p) {
     constexpr int NK = SL * REC_SPLIT;             // key channels the registers hold (dk <= NK)
     constexpr int TOK = NK > 128 ? 8 : 16;
     constexpr bool BONUS_IN_REGS = SL <= 32;
-    constexpr bool UNI = MODE == REC_FIXED;        // one decay for the whole head: a register, no row of shared memory
+    constexpr bool UNI = MODE == REC_FIXED || MODE == REC_SSD;   // one decay for the whole head: a register, no row of shared memory
+    __shared__ float s_wt[TOK], s_dt[TOK];         // REC_SSD: the token's decay and step, formed once per token
     // A warp's four parts read their channels at the same moment, SL floats apart: every part's channels sit four floats
     // further on than the part before, so that the four 16-byte reads fall into different banks (SL = 32: banks 0, 4, 8, 12
     // in place of four times bank 0).
@@ -156,7 +157,7 @@ linear_recurrence_kernel(RecParams p) {
     const bool owns = j < p.dv;
     const int i0 = part * SL;
     float S[SL], ub[BONUS_IN_REGS ? SL : 1], D[(BLOCKS && !UNI) ? SL : 1];
-    const float wuni = UNI ? p.c0.at(head) : 0.f;
+    const float wuni = MODE == REC_FIXED ? p.c0.at(head) : 0.f;
     float* st = BLOCKS ? p.s_loc + ((size_t)blockIdx.x * p.H + head) * dk * p.dv + j
                        : p.state + (size_t)slot * p.state_stride + (size_t)head * dk * p.dv + j;
 #pragma unroll
@@ -216,11 +217,14 @@ linear_recurrence_kernel(RecParams p) {
                         kv = rk[f];
                         wv = expf(p.c1.at(hc + i) * logsig);
                     } else if (MODE == REC_SSD) {
-                        const float z = rg[f] + p.c1.at(head);
-                        const float dt = fmaxf(z, 0.f) + log1pf(expf(-fabsf(z)));
                         qv = rq[f];
-                        kv = rk[f] * dt;
-                        wv = expf(-expf(p.c0.at(head)) * dt);
+                        kv = rk[f];       // the step multiplies the token's values once instead of every key channel
+                        if (i == 0) {
+                            const float z = rg[f] + p.c1.at(head);
+                            const float dt = fmaxf(z, 0.f) + log1pf(expf(-fabsf(z)));
+                            s_dt[u] = dt;
+                            s_wt[u] = expf(-expf(p.c0.at(head)) * dt);
+                        }
                     } else {
                         const float l = p.c1.at(hc + i);
                         const float fg = l + (1.0f - l) * (1.0f / (1.0f + expf(-(rg[f] + p.c0.at(hc + i)))));
@@ -245,14 +249,15 @@ linear_recurrence_kernel(RecParams p) {
         __syncthreads();
         if (t0 + tok < row1) fetch(t0 + tok, min(tok, row1 - t0 - tok));
         for (int u = 0; u < nt; ++u) {
-            const float vj = sv[u][cj];
+            const float vj = MODE == REC_SSD ? sv[u][cj] * s_dt[u] : sv[u][cj];
+            const float wt = MODE == REC_SSD ? s_wt[u] : wuni;
             float acc0 = 0.f, acc1 = 0.f;
-            if (BLOCKS && UNI) D[0] *= wuni;   // the output looks at the state after the token's own decay
+            if (BLOCKS && UNI) D[0] *= wt;   // the output looks at the state after the token's own decay
 #pragma unroll
             for (int i4 = 0; i4 < SL; i4 += 4) {
                 const float4 k4 = *reinterpret_cast<const float4*>(&sk[u][i0 + part * 4 + i4]);
                 const float4 q4 = *reinterpret_cast<const float4*>(&sq[u][i0 + part * 4 + i4]);
-                float4 w4 = make_float4(wuni, wuni, wuni, wuni);
+                float4 w4 = make_float4(wt, wt, wt, wt);
                 if (!UNI) w4 = *reinterpret_cast<const float4*>(&sw[u][i0 + part * 4 + i4]);
                 const float kk[4] = {k4.x, k4.y, k4.z, k4.w}, qq[4] = {q4.x, q4.y, q4.z, q4.w}, ww[4] = {w4.x, w4.y, w4.z, w4.w};
 #pragma unroll

@@ -568,51 +568,81 @@ struct CombineTerm {
 };
 struct CombineArgs { CombineTerm t[COMBINE_MAX_TERMS]; int n; };
 
-template <typename TO>
+template <typename TO, bool VEC>
 __global__ void __launch_bounds__(ROW_THREADS)
 combine_add_kernel(float* __restrict__ x, CombineArgs a, VecRef post_w, float post_eps, VecRef next_w, float next_eps,
                    TO* __restrict__ out, const int* __restrict__ rows, const int* __restrict__ tok_seq, int d) {
     __shared__ float red[32];
-    extern __shared__ float cbuf[];
+    extern __shared__ __align__(16) float cbuf[];
     float* acc = cbuf;        // d
     float* tmp = cbuf + d;    // d
     pdl_trigger();
     const int r = rows != nullptr ? rows[blockIdx.x] : blockIdx.x;
     pdl_wait();
     if (tok_seq != nullptr && tok_seq[r] < 0) return;
-    for (int j = threadIdx.x; j < d; j += blockDim.x) acc[j] = 0.f;
+    // VEC: four elements at a time (the width a multiple of four, every row 16-byte aligned); the same sums either way
+    constexpr int W = VEC ? 4 : 1;
+    const int j0 = threadIdx.x * W, dj = blockDim.x * W;
+    auto load = [&](const CombineTerm& tm, size_t at, float* v) {
+        if (VEC) {
+            const float4 q = tm.is_bf16 ? ld4((const bf16*)tm.p + at) : ld4((const float*)tm.p + at);
+            v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w;
+        } else {
+            v[0] = tm.is_bf16 ? __bfloat162float(((const bf16*)tm.p)[at]) : ((const float*)tm.p)[at];
+        }
+    };
+    auto weights = [&](const VecRef& w, int j, float* v) {
+        if (VEC) { const float4 q = w.at4(j); v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w; }
+        else v[0] = w.at(j);
+    };
     for (int i = 0; i < a.n; ++i) {
         const CombineTerm& tm = a.t[i];
         float ss = 0.f;
-        for (int j = threadIdx.x; j < d; j += blockDim.x) {
-            float v = 0.f;
+        for (int j = j0; j < d; j += dj) {
+            float v[W], u[W];
+#pragma unroll
+            for (int e = 0; e < W; ++e) v[e] = 0.f;
             for (int sp = 0; sp < tm.n_split; ++sp) {
-                const size_t at = (size_t)sp * tm.split_stride + (size_t)r * d + j;
-                v += tm.is_bf16 ? __bfloat162float(((const bf16*)tm.p)[at]) : ((const float*)tm.p)[at];
+                load(tm, (size_t)sp * tm.split_stride + (size_t)r * d + j, u);
+#pragma unroll
+                for (int e = 0; e < W; ++e) v[e] += u[e];
             }
-            tmp[j] = v;
-            ss += v * v;
+#pragma unroll
+            for (int e = 0; e < W; ++e) { tmp[j + e] = v[e]; ss += v[e] * v[e]; }
         }
         float f = tm.scale;
         if (tm.row_scale != nullptr) f *= tm.row_scale[r];
+        float rs = 1.0f;
         if (tm.norm_w.p != nullptr) {
             ss = block_sum(ss, red);
             ss /= (float)d;
             ss += tm.norm_eps;
-            const float rs = 1.0f / sqrtf(ss);
-            for (int j = threadIdx.x; j < d; j += blockDim.x) acc[j] += f * (tm.norm_w.at(j) * (rs * tmp[j]));
-        } else {
-            for (int j = threadIdx.x; j < d; j += blockDim.x) acc[j] += f * tmp[j];
+            rs = 1.0f / sqrtf(ss);
+        }
+        for (int j = j0; j < d; j += dj) {
+            float w[W];
+            if (tm.norm_w.p != nullptr) weights(tm.norm_w, j, w);
+#pragma unroll
+            for (int e = 0; e < W; ++e) {
+                const float v = tm.norm_w.p != nullptr ? f * (w[e] * (rs * tmp[j + e])) : f * tmp[j + e];
+                acc[j + e] = i == 0 ? v : acc[j + e] + v;
+            }
         }
     }
-    if (x == nullptr) {
-        for (int j = threadIdx.x; j < d; j += blockDim.x) out[(size_t)blockIdx.x * d + j] = from_f32<TO>(acc[j]);
+    if (x == nullptr) {   // every thread hands on the elements that it summed itself
+        for (int j = j0; j < d; j += dj) {
+#pragma unroll
+            for (int e = 0; e < W; ++e) out[(size_t)blockIdx.x * d + j + e] = from_f32<TO>(acc[j + e]);
+        }
         return;
     }
     float rs = 1.0f;
     if (post_w.p != nullptr) {
         float ss = 0.f;
-        for (int j = threadIdx.x; j < d; j += blockDim.x) ss += acc[j] * acc[j];
+        for (int j = j0; j < d; j += dj) {
+#pragma unroll
+            for (int e = 0; e < W; ++e) ss += acc[j + e] * acc[j + e];
+        }
         ss = block_sum(ss, red);
         ss /= (float)d;
         ss += post_eps;
@@ -620,19 +650,34 @@ combine_add_kernel(float* __restrict__ x, CombineArgs a, VecRef post_w, float po
     }
     float* xr = x + (size_t)r * d;
     float s2 = 0.f;
-    for (int j = threadIdx.x; j < d; j += blockDim.x) {
-        const float v = xr[j] + (post_w.p != nullptr ? post_w.at(j) * (rs * acc[j]) : acc[j]);
-        if (rows == nullptr) xr[j] = v;
-        tmp[j] = v;
-        s2 += v * v;
+    for (int j = j0; j < d; j += dj) {
+        float xv[W], w[W];
+        if (VEC) { const float4 q = ld4(xr + j); xv[0] = q.x; xv[1] = q.y; xv[2] = q.z; xv[3] = q.w; }
+        else xv[0] = xr[j];
+        if (post_w.p != nullptr) weights(post_w, j, w);
+#pragma unroll
+        for (int e = 0; e < W; ++e) {
+            xv[e] += post_w.p != nullptr ? w[e] * (rs * acc[j + e]) : acc[j + e];
+            tmp[j + e] = xv[e];
+            s2 += xv[e] * xv[e];
+        }
+        if (rows == nullptr) {
+            if (VEC) st4(xr + j, make_float4(xv[0], xv[1], xv[2], xv[3]));
+            else xr[j] = xv[0];
+        }
     }
     if (next_w.p == nullptr) return;
     s2 = block_sum(s2, red);
     s2 /= (float)d;
     s2 += next_eps;
     const float r2 = 1.0f / sqrtf(s2);
-    for (int j = threadIdx.x; j < d; j += blockDim.x)
-        out[(size_t)blockIdx.x * d + j] = from_f32<TO>(next_w.at(j) * (r2 * tmp[j]));
+    TO* orow = out + (size_t)blockIdx.x * d;
+    for (int j = j0; j < d; j += dj) {
+        float w[W];
+        weights(next_w, j, w);
+        if (VEC) st4(orow + j, make_float4(w[0] * (r2 * tmp[j]), w[1] * (r2 * tmp[j + 1]), w[2] * (r2 * tmp[j + 2]), w[3] * (r2 * tmp[j + 3])));
+        else orow[j] = from_f32<TO>(w[0] * (r2 * tmp[j]));
+    }
 }
 
 extern "C" int odin_combine_add(float* x, int n_terms, const void* const* ptrs, const int* dtypes, const int* n_splits,
@@ -649,22 +694,27 @@ extern "C" int odin_combine_add(float* x, int n_terms, const void* const* ptrs, 
     if (smem > 200 * 1024) return ODIN_ERR_UNSUPPORTED;
     CombineArgs a;
     a.n = n_terms;
+    uintptr_t all_bits = 0;
     for (int i = 0; i < n_terms; ++i) {
         if (dtypes[i] != ODIN_BF16 && dtypes[i] != ODIN_F32) return ODIN_ERR_UNSUPPORTED;
         a.t[i].p = ptrs[i]; a.t[i].is_bf16 = dtypes[i] == ODIN_BF16; a.t[i].n_split = n_splits[i];
         a.t[i].split_stride = split_strides[i]; a.t[i].scale = scales[i]; a.t[i].row_scale = row_scales[i];
         a.t[i].norm_w = VecRef{norm_ws[i], norm_w_dtypes[i] == ODIN_BF16}; a.t[i].norm_eps = norm_eps[i];
+        all_bits |= (uintptr_t)ptrs[i] | (uintptr_t)norm_ws[i] | (uintptr_t)(split_strides[i] * 4);
     }
+    all_bits |= (uintptr_t)x | (uintptr_t)out | (uintptr_t)post_w | (uintptr_t)next_w;
+    const bool vec = (d % 4 == 0) && (all_bits % 16 == 0);
     cudaStream_t s = (cudaStream_t)stream;
     VecRef pw{post_w, post_w_dtype == ODIN_BF16}, nw{next_w, next_w_dtype == ODIN_BF16};
 #define GO(TO)                                                                                                       \
     do {                                                                                                             \
+        auto kern = vec ? combine_add_kernel<TO, true> : combine_add_kernel<TO, false>;                              \
         if (smem > 48 * 1024) {                                                                                      \
-            cudaError_t e = cudaFuncSetAttribute(combine_add_kernel<TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);       \
             if (e != cudaSuccess) return (int)e;                                                                     \
         }                                                                                                            \
-        odin_launch(combine_add_kernel<TO>, dim3(n_rows), dim3(ROW_THREADS), smem, s, x, a, pw, post_eps, nw, next_eps, \
-                    (TO*)out, rows, tok_seq, d);                                                                     \
+        odin_launch(kern, dim3(n_rows), dim3(ROW_THREADS), smem, s, x, a, pw, post_eps, nw, next_eps, (TO*)out, rows,   \
+                    tok_seq, d);                                                                                     \
     } while (0)
     if (out == nullptr || out_dtype == ODIN_F32) GO(float);
     else if (out_dtype == ODIN_BF16) GO(bf16);

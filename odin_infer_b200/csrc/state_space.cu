@@ -45,6 +45,58 @@ causal_conv_kernel(const TI* __restrict__ in, size_t in_stride, VecRef w, VecRef
     out[(size_t)t * out_stride + c] = from_f32<TO>(silu ? ss_silu(acc) : acc);
 }
 
+// Up to four taps: a thread takes one channel over CONV_TOK rows in turn, its weights and the last three inputs in
+// registers, so that a row costs one load and one store (the window is fetched anew where a sequence's rows begin).
+// The same sum in the same order as above (a tap that the filter does not have multiplies nothing and is left out).
+#define CONV_TOK 16
+template <typename TI, typename TO>
+__global__ void __launch_bounds__(256)
+causal_conv4_kernel(const TI* __restrict__ in, size_t in_stride, VecRef w, VecRef bias, int taps, int silu,
+                    const float* __restrict__ state, size_t state_stride, const int* __restrict__ tok_seq,
+                    const int* __restrict__ seq_start, const int* __restrict__ seq_slots, TO* __restrict__ out,
+                    size_t out_stride, int C, int T) {
+    pdl_trigger();
+    const int t0 = blockIdx.x * CONV_TOK, t1 = min(T, t0 + CONV_TOK);
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    float wv[4] = {0.f, 0.f, 0.f, 0.f};   // wv[3] meets the current row, wv[3 - m] the row m before
+    float b = 0.f;
+    if (c < C) {
+        for (int j = 0; j < taps; ++j) wv[4 - taps + j] = w.at(c * taps + j);
+        if (bias.p != nullptr) b = bias.at(c);
+    }
+    pdl_wait();
+    if (c >= C) return;
+    float win[3] = {0.f, 0.f, 0.f};       // win[m - 1]: the input m rows before
+    int have = -1;                        // the sequence whose rows the window holds
+    for (int t = t0; t < t1; ++t) {
+        const int seq = tok_seq[t];
+        if (seq < 0) { have = -1; continue; }
+        const int first = seq_start[seq];
+        if (seq != have || t == first) {
+            const int slot = seq_slots[seq];
+#pragma unroll
+            for (int m = 1; m <= 3; ++m) {
+                float v = 0.f;
+                if (m < taps) {
+                    const int r = t - m;
+                    v = r >= first ? to_f32(in[(size_t)r * in_stride + c])
+                                   : state[(size_t)slot * state_stride + (size_t)(taps - 1 - (first - r)) * C + c];
+                }
+                win[m - 1] = v;
+            }
+            have = seq;
+        }
+        const float cur = to_f32(in[(size_t)t * in_stride + c]);
+        float acc = b;
+        if (taps > 3) acc = fmaf(wv[0], win[2], acc);
+        if (taps > 2) acc = fmaf(wv[1], win[1], acc);
+        if (taps > 1) acc = fmaf(wv[2], win[0], acc);
+        acc = fmaf(wv[3], cur, acc);
+        out[(size_t)t * out_stride + c] = from_f32<TO>(silu ? ss_silu(acc) : acc);
+        win[2] = win[1]; win[1] = win[0]; win[0] = cur;
+    }
+}
+
 // state[slot] <- the last taps - 1 inputs of (old state ++ the step's rows).  grid (sequences, channel blocks).
 template <typename TI>
 __global__ void __launch_bounds__(256)
@@ -75,10 +127,18 @@ extern "C" int odin_causal_conv(const void* in, int in_dtype, long long in_strid
     const int threads = C >= 256 ? 256 : (C + 31) / 32 * 32;
     dim3 grid(T, (C + threads - 1) / threads);
     if (grid.y > 65535) return ODIN_ERR_UNSUPPORTED;
+    const dim3 grid4((T + CONV_TOK - 1) / CONV_TOK, grid.y);
 #define GO(TI, TO)                                                                                                   \
-    odin_launch(causal_conv_kernel<TI, TO>, grid, dim3(threads), 0, s, (const TI*)in, (size_t)in_stride, wv, bv, taps, \
-                silu, (const float*)state, (size_t)state_stride, tok_seq, seq_start, seq_slots, (TO*)out,             \
-                (size_t)out_stride, C)
+    do {                                                                                                             \
+        if (taps <= 4 && T > 64)                                                                                     \
+            odin_launch(causal_conv4_kernel<TI, TO>, grid4, dim3(threads), 0, s, (const TI*)in, (size_t)in_stride, wv, bv, \
+                        taps, silu, (const float*)state, (size_t)state_stride, tok_seq, seq_start, seq_slots, (TO*)out, \
+                        (size_t)out_stride, C, T);                                                                   \
+        else                                                                                                         \
+            odin_launch(causal_conv_kernel<TI, TO>, grid, dim3(threads), 0, s, (const TI*)in, (size_t)in_stride, wv, bv, \
+                        taps, silu, (const float*)state, (size_t)state_stride, tok_seq, seq_start, seq_slots, (TO*)out, \
+                        (size_t)out_stride, C);                                                                      \
+    } while (0)
     if (in_dtype == ODIN_BF16 && out_dtype == ODIN_BF16) GO(bf16, bf16);
     else if (in_dtype == ODIN_BF16 && out_dtype == ODIN_F32) GO(bf16, float);
     else if (in_dtype == ODIN_F32 && out_dtype == ODIN_F32) GO(float, float);
@@ -117,9 +177,18 @@ struct ScanParams {
     void* out; int out_is_bf16; long long out_stride;
     const int* seq_start; const int* seq_slots;
     int inner, N;
+    // Blocks of tokens (block_len > 0): a CTA walks one block of one sequence from a state of zeros and leaves the block's
+    // own state in s_loc, the sum of its step sizes per channel in dtot, per token the sum since the block's start in cumdt
+    // and the output so far (before the gate) in ytmp; a second kernel carries the state from block to block, a third adds
+    // what each block's incoming state contributes to its tokens' outputs and applies the gate.
+    int block_len, n_blocks;
+    float* ytmp;    // [rows, inner]
+    float* cumdt;   // [rows, inner]
+    float* s_loc;   // [sequences * n_blocks][inner][N]
+    float* dtot;    // [sequences * n_blocks][inner]
 };
 
-template <int NPL>
+template <int NPL, bool BLOCKS>
 __global__ void __launch_bounds__(SCAN_CH * SCAN_LANES)
 selective_scan_kernel(ScanParams p) {
     extern __shared__ float scan_sm[];
@@ -130,11 +199,14 @@ selective_scan_kernel(ScanParams p) {
     float* sdt = sx + SCAN_TOK * SCAN_CH;
     float* sz = sdt + SCAN_TOK * SCAN_CH;
     pdl_trigger();
-    const int b = blockIdx.x, ch0 = blockIdx.y * SCAN_CH;
+    const int b = BLOCKS ? blockIdx.x / p.n_blocks : blockIdx.x, ch0 = blockIdx.y * SCAN_CH;
     const int cl = threadIdx.x / SCAN_LANES, l = threadIdx.x % SCAN_LANES;
     const int c = ch0 + cl;
     const bool live = c < p.inner;
-    const int row0 = p.seq_start[b], row1 = p.seq_start[b + 1], slot = p.seq_slots[b];
+    const int seq_end = p.seq_start[b + 1];
+    const int row0 = p.seq_start[b] + (BLOCKS ? (int)(blockIdx.x % p.n_blocks) * p.block_len : 0);
+    const int row1 = BLOCKS ? min(seq_end, row0 + p.block_len) : seq_end;
+    const int slot = p.seq_slots[b];
     float A[NPL], S[NPL];
 #pragma unroll
     for (int j = 0; j < NPL; ++j) {
@@ -144,12 +216,14 @@ selective_scan_kernel(ScanParams p) {
     const float Dc = (live && p.D.p != nullptr) ? p.D.at(c) : 0.f;
     pdl_wait();
     if (row1 <= row0) return;   // an empty (padding) sequence owns no state
-    float* st = p.state + (size_t)slot * p.state_stride + (size_t)c * N;
+    float* st = BLOCKS ? p.s_loc + ((size_t)blockIdx.x * p.inner + c) * N
+                       : p.state + (size_t)slot * p.state_stride + (size_t)c * N;
 #pragma unroll
     for (int j = 0; j < NPL; ++j) {
         const int n = l + SCAN_LANES * j;
-        S[j] = (live && n < N) ? st[n] : 0.f;
+        S[j] = (!BLOCKS && live && n < N) ? st[n] : 0.f;
     }
+    float cum = 0.f;
     for (int t0 = row0; t0 < row1; t0 += SCAN_TOK) {
         const int nt = min(SCAN_TOK, row1 - t0);
         __syncthreads();   // the block before has been walked
@@ -185,11 +259,17 @@ selective_scan_kernel(ScanParams p) {
             }
             acc += __shfl_xor_sync(0xffffffffu, acc, 1);
             acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+            if (BLOCKS) cum += dt;
             if (live && l == 0) {
                 float y = fmaf(Dc, xv, acc);
-                if (p.z != nullptr) y *= ss_silu(sz[u * SCAN_CH + cl]);
-                const size_t o = (size_t)(t0 + u) * p.out_stride + c;
-                if (p.out_is_bf16) ((bf16*)p.out)[o] = __float2bfloat16_rn(y); else ((float*)p.out)[o] = y;
+                if (BLOCKS) {
+                    p.ytmp[(size_t)(t0 + u) * p.inner + c] = y;
+                    p.cumdt[(size_t)(t0 + u) * p.inner + c] = cum;
+                } else {
+                    if (p.z != nullptr) y *= ss_silu(sz[u * SCAN_CH + cl]);
+                    const size_t o = (size_t)(t0 + u) * p.out_stride + c;
+                    if (p.out_is_bf16) ((bf16*)p.out)[o] = __float2bfloat16_rn(y); else ((float*)p.out)[o] = y;
+                }
             }
         }
     }
@@ -198,15 +278,101 @@ selective_scan_kernel(ScanParams p) {
         const int n = l + SCAN_LANES * j;
         if (live && n < N) st[n] = S[j];
     }
+    if (BLOCKS && live && l == 0) p.dtot[(size_t)blockIdx.x * p.inner + c] = cum;
+}
+
+// The state from block to block: S_in(first block) = the sequence's state; S_in(next) = exp(A dtot) S_in + s_loc.
+// s_loc is overwritten with S_in (what the block's tokens look at); the last S becomes the sequence's state.
+__global__ void __launch_bounds__(256)
+scan_carry_kernel(ScanParams p) {
+    pdl_trigger();
+    const int b = blockIdx.x;
+    const int e = blockIdx.y * blockDim.x + threadIdx.x;   // (channel, state index)
+    const int row0 = p.seq_start[b], row1 = p.seq_start[b + 1], slot = p.seq_slots[b];
+    pdl_wait();
+    if (row1 <= row0 || e >= p.inner * p.N) return;
+    const int c = e / p.N;
+    const float A = -expf(p.A_log.at(e));
+    float* st = p.state + (size_t)slot * p.state_stride + e;
+    float S = *st;
+    const int n = (row1 - row0 + p.block_len - 1) / p.block_len;
+    for (int k = 0; k < n; ++k) {
+        const size_t item = (size_t)b * p.n_blocks + k;
+        const float own = p.s_loc[item * p.inner * p.N + e];
+        p.s_loc[item * p.inner * p.N + e] = S;
+        S = fmaf(expf(A * p.dtot[item * p.inner + c]), S, own);
+    }
+    *st = S;
+}
+
+// out[t, c] = (ytmp[t, c] + sum_n C_t[n] exp(A[c, n] cumdt[t, c]) S_in[c, n]) * silu(z[t, c]) for the tokens of one block.
+template <int NPL>
+__global__ void __launch_bounds__(SCAN_CH * SCAN_LANES)
+scan_carry_out_kernel(ScanParams p) {
+    extern __shared__ float scan_sm[];
+    const int N = p.N;
+    float* sC = scan_sm;   // [SCAN_TOK][N]
+    pdl_trigger();
+    const int item = blockIdx.x, b = item / p.n_blocks, ch0 = blockIdx.y * SCAN_CH;
+    const int cl = threadIdx.x / SCAN_LANES, l = threadIdx.x % SCAN_LANES;
+    const int c = ch0 + cl;
+    const bool live = c < p.inner;
+    const int seq_end = p.seq_start[b + 1];
+    const int row0 = p.seq_start[b] + (item % p.n_blocks) * p.block_len;
+    const int row1 = min(seq_end, row0 + p.block_len);
+    float A[NPL], Sin[NPL];
+#pragma unroll
+    for (int j = 0; j < NPL; ++j) {
+        const int n = l + SCAN_LANES * j;
+        A[j] = (live && n < N) ? -expf(p.A_log.at(c * N + n)) : 0.f;
+    }
+    pdl_wait();
+    if (row1 <= row0) return;
+#pragma unroll
+    for (int j = 0; j < NPL; ++j) {
+        const int n = l + SCAN_LANES * j;
+        Sin[j] = (live && n < N) ? p.s_loc[((size_t)item * p.inner + c) * N + n] : 0.f;
+    }
+    for (int t0 = row0; t0 < row1; t0 += SCAN_TOK) {
+        const int nt = min(SCAN_TOK, row1 - t0);
+        __syncthreads();
+        for (int e = threadIdx.x; e < nt * N; e += blockDim.x) sC[e] = p.C[(size_t)(t0 + e / N) * p.bc_stride + e % N];
+        __syncthreads();
+        for (int u = 0; u < nt; ++u) {
+            const size_t r = (size_t)(t0 + u);
+            const float cd = live ? p.cumdt[r * p.inner + c] : 0.f;
+            float acc = 0.f;
+#pragma unroll
+            for (int j = 0; j < NPL; ++j) {
+                const int n = l + SCAN_LANES * j;
+                if (n < N) acc = fmaf(expf(cd * A[j]) * Sin[j], sC[u * N + n], acc);
+            }
+            acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+            acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+            if (live && l == 0) {
+                float y = p.ytmp[r * p.inner + c] + acc;
+                if (p.z != nullptr) {
+                    const float zv = p.x_is_bf16 ? __bfloat162float(((const bf16*)p.z)[r * p.z_stride + c]) : ((const float*)p.z)[r * p.z_stride + c];
+                    y *= ss_silu(zv);
+                }
+                const size_t o = r * p.out_stride + c;
+                if (p.out_is_bf16) ((bf16*)p.out)[o] = __float2bfloat16_rn(y); else ((float*)p.out)[o] = y;
+            }
+        }
+    }
 }
 
 extern "C" int odin_selective_scan(const void* x, int x_dtype, long long x_stride, const float* dt, long long dt_stride,
                                    const void* dt_bias, const float* B, const float* C, long long bc_stride,
                                    const void* A_log, const void* D, int w_dtype, const void* z, long long z_stride,
                                    float* state, long long state_stride, void* out, int out_dtype, long long out_stride,
-                                   const int* seq_start, const int* seq_slots, int n_seqs, int inner, int N, void* stream) {
+                                   const int* seq_start, const int* seq_slots, int n_seqs, int inner, int N, int block_len,
+                                   int n_blocks, float* ytmp, float* cumdt, float* s_loc, float* dtot, void* stream) {
     if (n_seqs <= 0) return 0;
     if (inner <= 0 || N <= 0 || N > 32 * SCAN_LANES) return ODIN_ERR_UNSUPPORTED;
+    if (block_len < 0 || (block_len > 0 && (n_blocks <= 0 || ytmp == nullptr || cumdt == nullptr || s_loc == nullptr ||
+                                            dtot == nullptr || (long long)n_seqs * n_blocks > 2147483647LL)))
+        return ODIN_ERR_BAD_ARG;
     ScanParams p;
     p.x = x; p.x_is_bf16 = x_dtype == ODIN_BF16; p.x_stride = x_stride;
     p.dt = dt; p.dt_stride = dt_stride; p.dt_bias = VecRef{dt_bias, w_dtype == ODIN_BF16};
@@ -215,49 +381,66 @@ extern "C" int odin_selective_scan(const void* x, int x_dtype, long long x_strid
     p.z = z; p.z_stride = z_stride; p.state = state; p.state_stride = state_stride;
     p.out = out; p.out_is_bf16 = out_dtype == ODIN_BF16; p.out_stride = out_stride;
     p.seq_start = seq_start; p.seq_slots = seq_slots; p.inner = inner; p.N = N;
+    p.block_len = block_len; p.n_blocks = n_blocks; p.ytmp = ytmp; p.cumdt = cumdt; p.s_loc = s_loc; p.dtot = dtot;
     cudaStream_t s = (cudaStream_t)stream;
-    dim3 grid(n_seqs, (inner + SCAN_CH - 1) / SCAN_CH);
+    const bool blocks = block_len > 0;
+    dim3 grid(blocks ? n_seqs * n_blocks : n_seqs, (inner + SCAN_CH - 1) / SCAN_CH);
     if (grid.y > 65535) return ODIN_ERR_UNSUPPORTED;
     const size_t smem = (size_t)(2 * SCAN_TOK * N + 3 * SCAN_TOK * SCAN_CH) * sizeof(float);
     const dim3 block(SCAN_CH * SCAN_LANES);
-    if (N <= 16) odin_launch(selective_scan_kernel<4>, grid, block, smem, s, p);
-    else if (N <= 32) odin_launch(selective_scan_kernel<8>, grid, block, smem, s, p);
-    else if (N <= 64) odin_launch(selective_scan_kernel<16>, grid, block, smem, s, p);
-    else odin_launch(selective_scan_kernel<32>, grid, block, smem, s, p);
+#define GO(NPL)                                                                                     \
+    do {                                                                                            \
+        if (blocks) odin_launch(selective_scan_kernel<NPL, true>, grid, block, smem, s, p);         \
+        else odin_launch(selective_scan_kernel<NPL, false>, grid, block, smem, s, p);               \
+    } while (0)
+    if (N <= 16) GO(4);
+    else if (N <= 32) GO(8);
+    else if (N <= 64) GO(16);
+    else GO(32);
+#undef GO
     ODIN_LAUNCH_CHECK();
+    if (blocks) {
+        odin_launch(scan_carry_kernel, dim3(n_seqs, (inner * N + 255) / 256), dim3(256), 0, s, p);
+        ODIN_LAUNCH_CHECK();
+        const size_t sm2 = (size_t)SCAN_TOK * N * sizeof(float);
+        if (N <= 16) odin_launch(scan_carry_out_kernel<4>, grid, block, sm2, s, p);
+        else if (N <= 32) odin_launch(scan_carry_out_kernel<8>, grid, block, sm2, s, p);
+        else if (N <= 64) odin_launch(scan_carry_out_kernel<16>, grid, block, sm2, s, p);
+        else odin_launch(scan_carry_out_kernel<32>, grid, block, sm2, s, p);
+        ODIN_LAUNCH_CHECK();
+    }
     return 0;
 }
 
 // ------------------------------------------------------------ skip, gate and grouped norm after a recurrence over heads
 // y[t, h, j] = (o[t, h, j] + D[h] x[t, h, j]) * silu(z[t, h, j]); the row is cut into `groups` equal consecutive parts and
-// every part is divided by its own root mean square; out = y * w.  One CTA per token; D, z and w are optional.
+// every part is divided by its own root mean square; out = y * w.  One CTA per (token, part); D, z and w are optional.
 template <typename TZ, typename TO>
 __global__ void __launch_bounds__(256)
 skip_gate_norm_kernel(const float* __restrict__ o, const float* __restrict__ x, size_t x_stride, VecRef D, int P,
                       const TZ* __restrict__ z, size_t z_stride, VecRef w, int groups, float eps, TO* __restrict__ out,
                       int inner) {
-    extern __shared__ float row[];   // inner
+    extern __shared__ float row[];   // one part of the row
     __shared__ float red[32];
     pdl_trigger();
     pdl_wait();
-    const int t = blockIdx.x;
-    for (int j = threadIdx.x; j < inner; j += blockDim.x) {
+    const int t = blockIdx.x, g = blockIdx.y;
+    const int gsz = inner / groups, j0 = g * gsz;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < gsz; i += blockDim.x) {
+        const int j = j0 + i;
         float y = o[(size_t)t * inner + j];
         if (D.p != nullptr) y = fmaf(D.at(j / P), x[(size_t)t * x_stride + j], y);
         if (z != nullptr) y *= ss_silu(to_f32(z[(size_t)t * z_stride + j]));
-        row[j] = y;
+        row[i] = y;
+        ss += y * y;
     }
-    const int gsz = inner / groups;
-    for (int g = 0; g < groups; ++g) {
-        float ss = 0.f;
-        for (int j = g * gsz + threadIdx.x; j < (g + 1) * gsz; j += blockDim.x) ss += row[j] * row[j];
-        ss = block_sum(ss, red);
-        ss /= (float)gsz;
-        ss += eps;
-        const float rs = 1.0f / sqrtf(ss);
-        for (int j = g * gsz + threadIdx.x; j < (g + 1) * gsz; j += blockDim.x)
-            out[(size_t)t * inner + j] = from_f32<TO>(w.p != nullptr ? w.at(j) * (rs * row[j]) : rs * row[j]);
-    }
+    ss = block_sum(ss, red);
+    ss /= (float)gsz;
+    ss += eps;
+    const float rs = 1.0f / sqrtf(ss);
+    for (int i = threadIdx.x; i < gsz; i += blockDim.x)
+        out[(size_t)t * inner + j0 + i] = from_f32<TO>(w.p != nullptr ? w.at(j0 + i) * (rs * row[i]) : rs * row[i]);
 }
 
 extern "C" int odin_skip_gate_norm(const float* o, const float* x, long long x_stride, const void* D, int P, const void* z,
@@ -265,17 +448,18 @@ extern "C" int odin_skip_gate_norm(const float* o, const float* x, long long x_s
                                    void* out, int out_dtype, int T, int inner, void* stream) {
     if (T <= 0) return 0;
     if (inner <= 0 || groups < 1 || inner % groups != 0 || P <= 0) return ODIN_ERR_BAD_ARG;
-    const size_t smem = (size_t)inner * sizeof(float);
-    if (smem > 200 * 1024) return ODIN_ERR_UNSUPPORTED;
+    const size_t smem = (size_t)(inner / groups) * sizeof(float);
+    if (smem > 200 * 1024 || groups > 65535) return ODIN_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
     VecRef Dv{D, w_dtype == ODIN_BF16}, wv{w, w_dtype == ODIN_BF16};
+    const int threads = inner / groups >= 1024 ? 256 : 128;
 #define GO(TZ, TO)                                                                                                      \
     do {                                                                                                                \
         if (smem > 48 * 1024) {                                                                                         \
             cudaError_t e = cudaFuncSetAttribute(skip_gate_norm_kernel<TZ, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
             if (e != cudaSuccess) return (int)e;                                                                        \
         }                                                                                                               \
-        odin_launch(skip_gate_norm_kernel<TZ, TO>, dim3(T), dim3(256), smem, s, o, x, (size_t)x_stride, Dv, P, (const TZ*)z, \
+        odin_launch(skip_gate_norm_kernel<TZ, TO>, dim3(T, groups), dim3(threads), smem, s, o, x, (size_t)x_stride, Dv, P, (const TZ*)z, \
                     (size_t)z_stride, wv, groups, eps, (TO*)out, inner);                                                \
     } while (0)
     if (z_dtype == ODIN_BF16 && out_dtype == ODIN_BF16) GO(bf16, bf16);

@@ -71,7 +71,7 @@ class SelectiveScan(Mixer):
         dt = rt.linear(low, self.w_dt, out_dtype=torch.float32)
         y = rt.empty(T, inner)
         ops.selective_scan(x, dt, self.dt_bias, bc[:, :N], bc[:, N:], self.A_log, self.D, xz[:, inner:], S, y,
-                           step.seq_start, step.seq_slots, step.n_seq_cap)
+                           step.seq_start, step.seq_slots, step.n_seq_cap, block_len=_block_len(step), max_new=step.max_new)
         return rt.linear(y, self.w_o, out_dtype=torch.float32, may_split=True)
 
 
