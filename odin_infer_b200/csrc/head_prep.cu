@@ -49,8 +49,10 @@ head_prep_kernel(const TI* qkv, int n_split, size_t split_stride, T* q_out,  // 
             const size_t wcol0 = side == 0 ? 0 : (size_t)Hq * hd;
             const TI* wsrc = qkv + (size_t)t * row_stride + wcol0;
             float sw = 0.f;
+#pragma unroll 2
             for (int j = threadIdx.x; j < whole; j += HP_WARPS * 32) {
                 float v = to_f32(wsrc[j]);
+#pragma unroll 4
                 for (int sp = 1; sp < n_split; ++sp) v += to_f32(wsrc[(size_t)sp * split_stride + j]);
                 if (bias.p != nullptr) v += bias.at((int)wcol0 + j);
                 sw += v * v;

@@ -333,14 +333,28 @@ scan_carry_out_kernel(ScanParams p) {
         const int n = l + SCAN_LANES * j;
         Sin[j] = (live && n < N) ? p.s_loc[((size_t)item * p.inner + c) * N + n] : 0.f;
     }
+    float* scd = sC + SCAN_TOK * N;            // [SCAN_TOK][SCAN_CH] sums of steps, outputs so far, gates
+    float* sy = scd + SCAN_TOK * SCAN_CH;
+    float* sz = sy + SCAN_TOK * SCAN_CH;
     for (int t0 = row0; t0 < row1; t0 += SCAN_TOK) {
         const int nt = min(SCAN_TOK, row1 - t0);
         __syncthreads();
         for (int e = threadIdx.x; e < nt * N; e += blockDim.x) sC[e] = p.C[(size_t)(t0 + e / N) * p.bc_stride + e % N];
+        for (int e = threadIdx.x; e < nt * SCAN_CH; e += blockDim.x) {
+            const int cc = ch0 + e % SCAN_CH;
+            const size_t r = (size_t)(t0 + e / SCAN_CH);
+            float cd = 0.f, yv = 0.f, zv = 0.f;
+            if (cc < p.inner) {
+                cd = p.cumdt[r * p.inner + cc];
+                yv = p.ytmp[r * p.inner + cc];
+                if (p.z != nullptr)
+                    zv = p.x_is_bf16 ? __bfloat162float(((const bf16*)p.z)[r * p.z_stride + cc]) : ((const float*)p.z)[r * p.z_stride + cc];
+            }
+            scd[e] = cd; sy[e] = yv; sz[e] = zv;
+        }
         __syncthreads();
         for (int u = 0; u < nt; ++u) {
-            const size_t r = (size_t)(t0 + u);
-            const float cd = live ? p.cumdt[r * p.inner + c] : 0.f;
+            const float cd = scd[u * SCAN_CH + cl];
             float acc = 0.f;
 #pragma unroll
             for (int j = 0; j < NPL; ++j) {
@@ -350,12 +364,9 @@ scan_carry_out_kernel(ScanParams p) {
             acc += __shfl_xor_sync(0xffffffffu, acc, 1);
             acc += __shfl_xor_sync(0xffffffffu, acc, 2);
             if (live && l == 0) {
-                float y = p.ytmp[r * p.inner + c] + acc;
-                if (p.z != nullptr) {
-                    const float zv = p.x_is_bf16 ? __bfloat162float(((const bf16*)p.z)[r * p.z_stride + c]) : ((const float*)p.z)[r * p.z_stride + c];
-                    y *= ss_silu(zv);
-                }
-                const size_t o = r * p.out_stride + c;
+                float y = sy[u * SCAN_CH + cl] + acc;
+                if (p.z != nullptr) y *= ss_silu(sz[u * SCAN_CH + cl]);
+                const size_t o = (size_t)(t0 + u) * p.out_stride + c;
                 if (p.out_is_bf16) ((bf16*)p.out)[o] = __float2bfloat16_rn(y); else ((float*)p.out)[o] = y;
             }
         }
@@ -369,7 +380,7 @@ extern "C" int odin_selective_scan(const void* x, int x_dtype, long long x_strid
                                    const int* seq_start, const int* seq_slots, int n_seqs, int inner, int N, int block_len,
                                    int n_blocks, float* ytmp, float* cumdt, float* s_loc, float* dtot, void* stream) {
     if (n_seqs <= 0) return 0;
-    if (inner <= 0 || N <= 0 || N > 32 * SCAN_LANES) return ODIN_ERR_UNSUPPORTED;
+    if (inner <= 0 || N <= 0 || N > 64 * SCAN_LANES) return ODIN_ERR_UNSUPPORTED;
     if (block_len < 0 || (block_len > 0 && (n_blocks <= 0 || ytmp == nullptr || cumdt == nullptr || s_loc == nullptr ||
                                             dtot == nullptr || (long long)n_seqs * n_blocks > 2147483647LL)))
         return ODIN_ERR_BAD_ARG;
@@ -396,17 +407,19 @@ extern "C" int odin_selective_scan(const void* x, int x_dtype, long long x_strid
     if (N <= 16) GO(4);
     else if (N <= 32) GO(8);
     else if (N <= 64) GO(16);
-    else GO(32);
+    else if (N <= 128) GO(32);
+    else GO(64);
 #undef GO
     ODIN_LAUNCH_CHECK();
     if (blocks) {
         odin_launch(scan_carry_kernel, dim3(n_seqs, (inner * N + 255) / 256), dim3(256), 0, s, p);
         ODIN_LAUNCH_CHECK();
-        const size_t sm2 = (size_t)SCAN_TOK * N * sizeof(float);
+        const size_t sm2 = (size_t)(SCAN_TOK * N + 3 * SCAN_TOK * SCAN_CH) * sizeof(float);
         if (N <= 16) odin_launch(scan_carry_out_kernel<4>, grid, block, sm2, s, p);
         else if (N <= 32) odin_launch(scan_carry_out_kernel<8>, grid, block, sm2, s, p);
         else if (N <= 64) odin_launch(scan_carry_out_kernel<16>, grid, block, sm2, s, p);
-        else odin_launch(scan_carry_out_kernel<32>, grid, block, sm2, s, p);
+        else if (N <= 128) odin_launch(scan_carry_out_kernel<32>, grid, block, sm2, s, p);
+        else odin_launch(scan_carry_out_kernel<64>, grid, block, sm2, s, p);
         ODIN_LAUNCH_CHECK();
     }
     return 0;

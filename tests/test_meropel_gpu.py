@@ -480,7 +480,7 @@ CUTS = lambda n: ([n], [2, 4, 7, 8, 64, 65, n - 3, n], list(range(n - 40, n + 1)
 
 
 SCAN_GEOMETRIES = [  # inner, state, dt_rank, taps, tokens
-    (48, 8, 4, 4, 150), (40, 33, 1, 2, 131), (72, 16, 6, 1, 90), (36, 70, 3, 5, 300), (256, 16, 8, 4, 520)]
+    (48, 8, 4, 4, 150), (40, 33, 1, 2, 131), (72, 16, 6, 1, 90), (36, 70, 3, 5, 300), (256, 16, 8, 4, 520), (24, 200, 2, 3, 270)]
 
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 3e-5), (torch.bfloat16, 3e-2)])
