@@ -44,15 +44,16 @@ head_prep_kernel(const TI* qkv, int n_split, size_t split_stride, T* q_out,  // 
     if (norm_mode == 3) {
         // the sums of squares of the token's whole q and whole k projection, by the CTA's warps together and in an order
         // that the sizes alone fix (every CTA of the token forms the same two sums)
+        // (only the sums that this CTA's four heads ask for: q heads come first, then k heads, then v heads)
+        const int h0 = blockIdx.y * HP_WARPS, h1 = min(n_heads, h0 + HP_WARPS);
         for (int side = 0; side < 2; ++side) {
+            if (side == 0 ? h0 >= Hq : (h1 <= Hq || h0 >= Hq + Hkv)) continue;
             const int whole = (side == 0 ? Hq : Hkv) * hd;
             const size_t wcol0 = side == 0 ? 0 : (size_t)Hq * hd;
             const TI* wsrc = qkv + (size_t)t * row_stride + wcol0;
             float sw = 0.f;
-#pragma unroll 2
             for (int j = threadIdx.x; j < whole; j += HP_WARPS * 32) {
                 float v = to_f32(wsrc[j]);
-#pragma unroll 4
                 for (int sp = 1; sp < n_split; ++sp) v += to_f32(wsrc[(size_t)sp * split_stride + j]);
                 if (bias.p != nullptr) v += bias.at((int)wcol0 + j);
                 sw += v * v;
