@@ -927,19 +927,19 @@ MEROPEL_SIZES = {
 
 def meropel_config(z: dict) -> dict:
     att = {"heads": z["heads"], "kv_heads": z["kv"], "dim": z["hd"], "vdim": z["hd"], "scale": z["hd"] ** -0.5}
-    par = {"left": dict(att, rot={"dims": z["hd"] // 2, "base": 10000.0}), "left_scale": 0.8, "right_scale": 0.5,
+    par = {"left": dict(att, rot={"dims": z["hd"] // 2, "base": 10000.0}), "left_scale": 0.7, "right_scale": 0.6,
            "right": {"inner": z["scan_inner"], "state": z["scan_state"], "dt_rank": z["dt_rank"], "conv": 4}}
     par2 = {"left": dict(att, rot={"dims": z["hd"], "base": 1000000.0}),
             "right": {"heads": z["ssd_heads"], "vdim": z["ssd_dim"], "state": z["ssd_state"], "groups": z["ssd_groups"],
                       "norm_groups": z["ssd_groups"], "conv": 4}}
-    gla = {"heads": z["gla_heads"], "dim": z["gla_dim"], "vdim": z["gla_v"], "tau": 16.0}
+    gla = {"heads": z["gla_heads"], "dim": z["gla_dim"], "vdim": z["gla_v"], "tau": 8.0}
     moe = {"kind": "moe", "expert": {"ff": z["eff"]}, "shared": {"ff": z["shared"]},
            "router": {"experts": z["experts"], "identity": z["identity"], "top": z["top"], "scale": 2.5,
                       "groups": {"count": z["groups"], "keep": z["keep"]}}}
     kinds = [("parallel", par), ("parallel_2", par2), ("gla", gla)]
     layers = [{"type": kinds[i % 3][0], "mixer": kinds[i % 3][1], "mlp": moe} for i in range(z["layers"])]
-    return {"architecture": "Meropel", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6}, "logit_scale": 0.25,
-            "embedding": {"bigram": {"buckets": 99991, "mul_prev": 127, "mul_cur": 7}}, "layers": layers}
+    return {"architecture": "Meropel", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6}, "logit_scale": 0.5,
+            "embedding": {"bigram": {"buckets": 99991, "mul_prev": 131, "mul_cur": 31}}, "layers": layers}
 
 
 def meropel_kernels(z: dict, T: int, peaks: dict) -> dict:
@@ -994,7 +994,7 @@ def meropel_kernels(z: dict, T: int, peaks: dict) -> dict:
     nb = T * d * (4 * 4 + 2)
     note("add + RMSNorm of two updates (nikonex)", timed(lambda: ops.row_update(x, [d1, d2], None, w1, 1e-6, 1, hb), flush), nbytes=nb)
     note("two terms with factors, their norm, the add, the next norm", timed(
-        lambda: ops.combine_add(x, [ops.Term(d1, 0.8), ops.Term(d2, 0.5)], w2, 1e-6, w1, 1e-6, hb), flush), nbytes=nb)
+        lambda: ops.combine_add(x, [ops.Term(d1, 0.7), ops.Term(d2, 0.6)], w2, 1e-6, w1, 1e-6, hb), flush), nbytes=nb)
     note("two terms each with a norm of its own, their norm, the add, the next norm", timed(
         lambda: ops.combine_add(x, [ops.Term(d1, 0.5, None, w1, 1e-6), ops.Term(d2, 0.5, None, w2, 1e-6)], w2, 1e-6, w1, 1e-6, hb), flush), nbytes=nb)
     # the embedding: a row of the token table, beside that plus a row of the pair table and the token before
@@ -1004,7 +1004,7 @@ def meropel_kernels(z: dict, T: int, peaks: dict) -> dict:
     before = torch.zeros(n_seq, 64, dtype=torch.int32, device=dev)
     note("embedding (nikonex)", timed(lambda: ops.embed(table, tok, x), flush), nbytes=T * d * 6)
     note("embedding plus the row of the pair (token before, token), two launches", timed(
-        lambda: ops.embed_pair(table, pairs, tok, seq, starts, slots, before, n_seq, buckets, 127, 7, x), flush), nbytes=T * d * 8)
+        lambda: ops.embed_pair(table, pairs, tok, seq, starts, slots, before, n_seq, buckets, 131, 31, x), flush), nbytes=T * d * 8)
     # head preparation: biases, the norm over the whole projection, rotation in pairs, beside the per-head norm
     Hq, Hkv, hd = z["heads"], z["kv"], z["hd"]
     kc = (torch.randn(n_pages, Hkv, 64, hd, device=dev) * 0.3).to(bf)
@@ -1052,7 +1052,7 @@ def meropel_kernels(z: dict, T: int, peaks: dict) -> dict:
     gstate = torch.zeros(n_seq, GH * gk * gv, device=dev)
     gq, gkk, graw = (torch.randn(T, GH * gk, device=dev) for _ in range(3))
     gvv, go = torch.randn(T, GH * gv, device=dev), torch.empty(T, GH * gv, device=dev)
-    gb, gt = torch.randn(GH * gk, device=dev) + 2, torch.full((GH * gk,), 1 / 16.0, device=dev)
+    gb, gt = torch.randn(GH * gk, device=dev) + 2, torch.full((GH * gk,), 1 / 8.0, device=dev)
     note(f"gated linear attention's recurrence ({GH} heads of {gk} x {gv})" + tag, timed(
         lambda: ops.linear_recurrence("gla", gq, gkk, graw, gvv, gb, gt, go, gstate, starts, slots, n_seq, GH, gk, gv, q_scale=gk ** -0.5, **blocks), flush),
         nbytes=rec_bytes(GH, gk, gv, 3 * GH * gk))

@@ -70,9 +70,9 @@ ODD = {"architecture": "Meropel", "vocab": 97, "width": 100, "norm": {"eps": 1e-
                   layer("parallel", par(attn(5, 1, 12, 20, 0.29, rot=12, base=50.0), 52, 40, 1, 5, 1.0, 1.0), None)]}
 # head sizes the tensor-core attention kernels take, widths the tensor-core products take
 FAST = {"architecture": "Meropel", "vocab": 512, "width": 128, "norm": {"eps": 1e-6}, "logit_scale": 0.5, "embedding": BIGRAM,
-        "layers": [layer("parallel", par(attn(4, 2, 64, 64, 0.125, rot=32), 256, 16, 8, 4, 0.8, 0.6), moe(8, 2, 2, 64, 5, 3, 1.5, shared=64)),
+        "layers": [layer("parallel", par(attn(4, 2, 64, 64, 0.11, rot=32), 256, 16, 8, 4, 0.9, 0.6), moe(7, 3, 2, 64, 5, 3, 1.25, shared=64)),
                    layer("parallel_2", par2(attn(2, 1, 128, 128, 0.09, rot=64, base=1e6), 8, 32, 64, 2, 2, 4), {"kind": "dense", "ff": 256}),
-                   layer("gla", {"heads": 2, "dim": 64, "vdim": 128, "tau": 16.0}, moe(16, 0, 4, 64, 4, 2, 1.0))]}
+                   layer("gla", {"heads": 2, "dim": 64, "vdim": 128, "tau": 12.0}, moe(16, 0, 4, 64, 4, 2, 1.0))]}
 CONFIGS = {"mixed": (MIXED, 3), "odd": (ODD, 5), "fast": (FAST, 7)}
 
 
