@@ -1003,8 +1003,8 @@ def meropel_kernels(z: dict, T: int, peaks: dict) -> dict:
     tok = torch.randint(0, V, (T,), dtype=torch.int32, device=dev)
     before = torch.zeros(n_seq, 64, dtype=torch.int32, device=dev)
     note("embedding (nikonex)", timed(lambda: ops.embed(table, tok, x), flush), nbytes=T * d * 6)
-    note("embedding plus the row of the pair (token before, token), two launches", timed(
-        lambda: ops.embed_pair(table, pairs, tok, seq, starts, slots, before, n_seq, buckets, 131, 31, x), flush), nbytes=T * d * 8)
+    note("embedding plus the row of the pair (token before, token), with its memory", timed(
+        lambda: ops.embed_pair(table, pairs, tok, seq, starts, slots, before, n_seq, buckets, 131, 31, x, single_rows=decode), flush), nbytes=T * d * 8)
     # head preparation: biases, the norm over the whole projection, rotation in pairs, beside the per-head norm
     Hq, Hkv, hd = z["heads"], z["kv"], z["hd"]
     kc = (torch.randn(n_pages, Hkv, 64, hd, device=dev) * 0.3).to(bf)
@@ -1027,8 +1027,8 @@ def meropel_kernels(z: dict, T: int, peaks: dict) -> dict:
     cw, cb = torch.randn(C, taps, device=dev).to(bf), torch.randn(C, device=dev).to(bf)
     cstate = torch.zeros(n_seq, (taps - 1) * C, device=dev)
     xc = torch.empty(T, C, dtype=bf, device=dev)
-    note(f"causal convolution of {taps} taps over {C} channels with SiLU, and its memory (two launches)", timed(
-        lambda: ops.causal_conv(xz[:, :C], cw, cb, True, cstate, seq, starts, slots, n_seq, xc), flush),
+    note(f"causal convolution of {taps} taps over {C} channels with SiLU, and its memory", timed(
+        lambda: ops.causal_conv(xz[:, :C], cw, cb, True, cstate, seq, starts, slots, n_seq, xc, single_rows=decode), flush),
         nbytes=T * C * 4 + 2 * n_seq * (taps - 1) * C * 4)
     # the recurrences: retention's (nikonex) beside the three of this design, decoding and a prompt
     RH, dk, dv = z["ret_heads"], z["ret_dim"], z["ret_v"]

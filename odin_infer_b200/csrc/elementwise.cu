@@ -44,9 +44,9 @@ extern "C" int odin_embed(const void* table, int table_dtype, const int* ids, fl
 template <typename TW>
 __global__ void embed_pair_kernel(const TW* __restrict__ table, const TW* __restrict__ pair, const int* __restrict__ ids,
                                   const int* __restrict__ tok_seq, const int* __restrict__ seq_start,
-                                  const int* __restrict__ seq_slots, const int* __restrict__ state, size_t state_stride,
+                                  const int* __restrict__ seq_slots, int* __restrict__ state, size_t state_stride,
                                   int buckets, long long mul_prev, long long mul_cur, float* __restrict__ out, int d, int V,
-                                  float scale) {
+                                  float scale, int store) {
     pdl_trigger();
     pdl_wait();
     const int t = blockIdx.x;
@@ -58,6 +58,10 @@ __global__ void embed_pair_kernel(const TW* __restrict__ table, const TW* __rest
         return;
     }
     const int before = t > seq_start[seq] ? ids[t - 1] + 1 : state[(size_t)seq_slots[seq] * state_stride];
+    if (store) {   // every sequence brings one row: its CTA has read the token before and stores this one in its place
+        __syncthreads();
+        if (threadIdx.x == 0) state[(size_t)seq_slots[seq] * state_stride] = id + 1;
+    }
     long long rowp = buckets;
     if (before > 0) rowp = (((long long)(before - 1) * mul_prev + (long long)id * mul_cur) % buckets + buckets) % buckets;
     const TW* row = table + (size_t)id * d;
@@ -79,21 +83,22 @@ __global__ void store_last_token_kernel(const int* __restrict__ ids, const int* 
 extern "C" int odin_embed_pair(const void* table, const void* pair, int table_dtype, const int* ids, const int* tok_seq,
                                const int* seq_start, const int* seq_slots, int* state, long long state_stride, int n_seqs,
                                int buckets, long long mul_prev, long long mul_cur, float* out, int T, int d, int V,
-                               float scale, void* stream) {
+                               float scale, int single_rows, void* stream) {
     if (T <= 0) return 0;
     if (buckets <= 0 || n_seqs <= 0) return ODIN_ERR_BAD_ARG;
     cudaStream_t s = (cudaStream_t)stream;
     const int threads = d >= 1024 ? 256 : 128;
     if (table_dtype == ODIN_BF16)
         odin_launch(embed_pair_kernel<bf16>, dim3(T), dim3(threads), 0, s, (const bf16*)table, (const bf16*)pair, ids, tok_seq,
-                    seq_start, seq_slots, (const int*)state, (size_t)state_stride, buckets, mul_prev, mul_cur, out, d, V, scale);
+                    seq_start, seq_slots, state, (size_t)state_stride, buckets, mul_prev, mul_cur, out, d, V, scale, single_rows);
     else if (table_dtype == ODIN_F32)
         odin_launch(embed_pair_kernel<float>, dim3(T), dim3(threads), 0, s, (const float*)table, (const float*)pair, ids,
-                    tok_seq, seq_start, seq_slots, (const int*)state, (size_t)state_stride, buckets, mul_prev, mul_cur, out, d,
-                    V, scale);
+                    tok_seq, seq_start, seq_slots, state, (size_t)state_stride, buckets, mul_prev, mul_cur, out, d,
+                    V, scale, single_rows);
     else
         return ODIN_ERR_UNSUPPORTED;
     ODIN_LAUNCH_CHECK();
+    if (single_rows) return 0;
     odin_launch(store_last_token_kernel, dim3((n_seqs + 127) / 128), dim3(128), 0, s, ids, seq_start, seq_slots, state,
                 (size_t)state_stride, n_seqs);
     ODIN_LAUNCH_CHECK();

@@ -86,11 +86,12 @@ def embed(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, scale: floa
 
 def embed_pair(table: torch.Tensor, pair: torch.Tensor, ids: torch.Tensor, tok_seq: torch.Tensor, seq_start: torch.Tensor,
                seq_slots: torch.Tensor, state: torch.Tensor, n_seqs: int, buckets: int, mul_prev: int, mul_cur: int,
-               out: torch.Tensor, scale: float = 1.0) -> None:
+               out: torch.Tensor, scale: float = 1.0, single_rows: bool = False) -> None:
     """out[t] = table[ids[t]] * scale + pair[(prev * mul_prev + ids[t] * mul_cur) mod buckets] as 32-bit floats, prev the
     token before in the sequence: the row above, or what `state` (int32 [slots, >= 1], any row stride) holds for the
     sequence's slot (token + 1; 0: the sequence starts here, and row `buckets` of `pair` stands in).  A second kernel
-    then stores every sequence's last token of this step in `state`.  Rows of sequence -1 become zeros."""
+    then stores every sequence's last token of this step in `state`.  Rows of sequence -1 become zeros.
+    single_rows: every sequence brings exactly one row; the one kernel then stores the token itself."""
     T, d = out.shape
     assert out.dtype == torch.float32 and out.is_contiguous() and ids.dtype == torch.int32
     assert table.shape[1] == d and tuple(pair.shape) == (buckets + 1, d) and pair.dtype == table.dtype
@@ -98,7 +99,8 @@ def embed_pair(table: torch.Tensor, pair: torch.Tensor, ids: torch.Tensor, tok_s
     _check(_fn("elementwise", "odin_embed_pair")(
         _ptr(table), _ptr(pair), c_int(dtype_code(table.dtype)), _ptr(ids), _ptr(tok_seq), _ptr(seq_start), _ptr(seq_slots),
         _ptr(state), c_longlong(state.stride(0)), c_int(n_seqs), c_int(buckets), c_longlong(mul_prev), c_longlong(mul_cur),
-        _ptr(out), c_int(T), c_int(d), c_int(table.shape[0]), c_float(scale), _stream()), "embed_pair", kernels=2)
+        _ptr(out), c_int(T), c_int(d), c_int(table.shape[0]), c_float(scale), c_int(1 if single_rows else 0), _stream()),
+        "embed_pair", kernels=1 if single_rows else 2)
 
 
 def add_rmsnorm(x: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor, eps: float,
@@ -583,11 +585,13 @@ def linear_recurrence(mode: str, q: torch.Tensor, k: torch.Tensor | None, g: tor
 
 
 def causal_conv(src: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, silu: bool, state: torch.Tensor,
-                tok_seq: torch.Tensor, seq_start: torch.Tensor, seq_slots: torch.Tensor, n_seqs: int, out: torch.Tensor) -> None:
+                tok_seq: torch.Tensor, seq_start: torch.Tensor, seq_slots: torch.Tensor, n_seqs: int, out: torch.Tensor,
+                single_rows: bool = False) -> None:
     """out[t, c] = act(bias[c] + sum_j weight[c, j] src[t - (taps - 1 - j), c]) over each sequence's rows (act: SiLU or
     none); the rows before a step's first one come from `state` (float32 [slots, >= (taps - 1) C], any row stride: the
     sequence's last taps - 1 inputs, oldest first; zeros at its start), into which a second kernel stores the step's last
-    inputs.  src: [T, C], a strided view is fine."""
+    inputs.  src: [T, C], a strided view is fine.  single_rows: every sequence brings exactly one row; the one kernel
+    then stores the memory itself."""
     T, C = out.shape
     taps = weight.shape[1]
     assert src.stride(1) == 1 and tuple(src.shape) == (T, C) and out.stride(1) == 1
@@ -599,8 +603,8 @@ def causal_conv(src: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | No
         _ptr(src), c_int(dtype_code(src.dtype)), c_longlong(src.stride(0)), _ptr(weight), c_int(dtype_code(weight.dtype)),
         _ptr(bias), c_int(dtype_code(bias.dtype) if bias is not None else 0), c_int(taps), c_int(1 if silu else 0),
         _ptr(state), c_longlong(state.stride(0)), _ptr(tok_seq), _ptr(seq_start), _ptr(seq_slots), c_int(n_seqs), _ptr(out),
-        c_int(dtype_code(out.dtype)), c_longlong(out.stride(0)), c_int(T), c_int(C), _stream()), "causal_conv",
-        kernels=2 if taps > 1 else 1)
+        c_int(dtype_code(out.dtype)), c_longlong(out.stride(0)), c_int(T), c_int(C), c_int(1 if single_rows else 0),
+        _stream()), "causal_conv", kernels=2 if (taps > 1 and not single_rows) else 1)
 
 
 def selective_scan(x: torch.Tensor, dt: torch.Tensor, dt_bias: torch.Tensor | None, B: torch.Tensor, C: torch.Tensor,

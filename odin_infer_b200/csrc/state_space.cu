@@ -20,12 +20,14 @@ __device__ __forceinline__ float ss_silu(float z) { return z / (1.0f + expf(-z))
 // ------------------------------------------------------------ causal convolution
 // out[t, c] = act(b[c] + sum_j w[c, j] * in[t - (taps - 1 - j), c]); rows before the sequence's first row of this step
 // are read from state[slot][taps - 1 - m][c] (m rows before).  grid (rows, channel blocks).
+// store: every sequence brings one row (a decode step), and the thread that has read its channel's memory writes the new one
+// itself (no other thread touches that channel of that slot); else a second kernel stores the memory.
 template <typename TI, typename TO>
 __global__ void __launch_bounds__(256)
 causal_conv_kernel(const TI* __restrict__ in, size_t in_stride, VecRef w, VecRef bias, int taps, int silu,
-                   const float* __restrict__ state, size_t state_stride, const int* __restrict__ tok_seq,
+                   float* __restrict__ state, size_t state_stride, const int* __restrict__ tok_seq,
                    const int* __restrict__ seq_start, const int* __restrict__ seq_slots, TO* __restrict__ out,
-                   size_t out_stride, int C) {
+                   size_t out_stride, int C, int store) {
     pdl_trigger();
     const int t = blockIdx.x;
     const int c = blockIdx.y * blockDim.x + threadIdx.x;
@@ -43,6 +45,11 @@ causal_conv_kernel(const TI* __restrict__ in, size_t in_stride, VecRef w, VecRef
         acc = fmaf(w.at(c * taps + j), v, acc);
     }
     out[(size_t)t * out_stride + c] = from_f32<TO>(silu ? ss_silu(acc) : acc);
+    if (store && taps > 1) {   // t == first: the memory moves up by one row and takes this row's input
+        float* st = state + (size_t)slot * state_stride + c;
+        for (int k = 0; k + 2 < taps; ++k) st[(size_t)k * C] = st[(size_t)(k + 1) * C];
+        st[(size_t)(taps - 2) * C] = to_f32(in[(size_t)t * in_stride + c]);
+    }
 }
 
 // Up to four taps: a thread takes one channel over CONV_TOK rows in turn, its weights and the last three inputs in
@@ -119,7 +126,7 @@ conv_state_kernel(const TI* __restrict__ in, size_t in_stride, int taps, float* 
 extern "C" int odin_causal_conv(const void* in, int in_dtype, long long in_stride, const void* w, int w_dtype,
                                 const void* bias, int bias_dtype, int taps, int silu, float* state, long long state_stride,
                                 const int* tok_seq, const int* seq_start, const int* seq_slots, int n_seqs, void* out,
-                                int out_dtype, long long out_stride, int T, int C, void* stream) {
+                                int out_dtype, long long out_stride, int T, int C, int single_rows, void* stream) {
     if (T <= 0) return 0;
     if (C <= 0 || taps < 1 || taps > 64 || n_seqs <= 0) return ODIN_ERR_BAD_ARG;
     cudaStream_t s = (cudaStream_t)stream;
@@ -130,14 +137,14 @@ extern "C" int odin_causal_conv(const void* in, int in_dtype, long long in_strid
     const dim3 grid4((T + CONV_TOK - 1) / CONV_TOK, grid.y);
 #define GO(TI, TO)                                                                                                   \
     do {                                                                                                             \
-        if (taps <= 4 && T > 64)                                                                                     \
+        if (taps <= 4 && T > 64 && !single_rows)                                                                     \
             odin_launch(causal_conv4_kernel<TI, TO>, grid4, dim3(threads), 0, s, (const TI*)in, (size_t)in_stride, wv, bv, \
                         taps, silu, (const float*)state, (size_t)state_stride, tok_seq, seq_start, seq_slots, (TO*)out, \
                         (size_t)out_stride, C, T);                                                                   \
         else                                                                                                         \
             odin_launch(causal_conv_kernel<TI, TO>, grid, dim3(threads), 0, s, (const TI*)in, (size_t)in_stride, wv, bv, \
-                        taps, silu, (const float*)state, (size_t)state_stride, tok_seq, seq_start, seq_slots, (TO*)out, \
-                        (size_t)out_stride, C);                                                                      \
+                        taps, silu, state, (size_t)state_stride, tok_seq, seq_start, seq_slots, (TO*)out,           \
+                        (size_t)out_stride, C, single_rows);                                                         \
     } while (0)
     if (in_dtype == ODIN_BF16 && out_dtype == ODIN_BF16) GO(bf16, bf16);
     else if (in_dtype == ODIN_BF16 && out_dtype == ODIN_F32) GO(bf16, float);
@@ -146,7 +153,7 @@ extern "C" int odin_causal_conv(const void* in, int in_dtype, long long in_strid
     else return ODIN_ERR_UNSUPPORTED;
 #undef GO
     ODIN_LAUNCH_CHECK();
-    if (taps > 1) {
+    if (taps > 1 && !single_rows) {
         dim3 g2(n_seqs, grid.y);
         if (in_dtype == ODIN_BF16)
             odin_launch(conv_state_kernel<bf16>, g2, dim3(threads), 0, s, (const bf16*)in, (size_t)in_stride, taps, state,

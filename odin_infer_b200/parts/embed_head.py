@@ -60,7 +60,8 @@ class TokenEmbedding(Embedding):
         if self.pair is not None:
             before = step.state(self.state_entry).view(torch.int32)
             ops.embed_pair(self.table, self.pair_table, step.tok_ids, step.tok_seq, step.seq_start, step.seq_slots, before,
-                           step.n_seq_cap, self.pair["buckets"], self.pair["mul_prev"], self.pair["mul_cur"], x, self.scale)
+                           step.n_seq_cap, self.pair["buckets"], self.pair["mul_prev"], self.pair["mul_cur"], x, self.scale,
+                           single_rows=step.all_single)
         else:
             ops.embed(self.table, step.tok_ids, x, self.scale)
         if self.norm is not None:

@@ -65,7 +65,7 @@ class SelectiveScan(Mixer):
         xz = rt.linear(h, self.w_in)
         x = rt.empty(T, inner)
         ops.causal_conv(xz[:, :inner], self.conv_w, self.conv_b, True, window, step.tok_seq, step.seq_start, step.seq_slots,
-                        step.n_seq_cap, x)
+                        step.n_seq_cap, x, single_rows=step.all_single)
         low = rt.linear(x, self.w_x_dt)
         bc = rt.linear(x, self.w_x_bc, out_dtype=torch.float32)
         dt = rt.linear(low, self.w_dt, out_dtype=torch.float32)
@@ -130,7 +130,7 @@ class StateSpaceDual(Mixer):
         proj = rt.linear(h, self.w_in, out_dtype=torch.float32)
         xbc = rt.empty(T, self.channels, dtype=torch.float32)
         ops.causal_conv(proj[:, inner:inner + self.channels], self.conv_w, self.conv_b, True, window, step.tok_seq,
-                        step.seq_start, step.seq_slots, step.n_seq_cap, xbc)
+                        step.seq_start, step.seq_slots, step.n_seq_cap, xbc, single_rows=step.all_single)
         x, B, C = xbc[:, :inner], xbc[:, inner:inner + GN], xbc[:, inner + GN:]
         o = rt.empty(T, inner, dtype=torch.float32)
         ops.linear_recurrence("ssd", C, B, proj[:, inner + self.channels:], x, self.A_log, self.dt_bias, o, S, step.seq_start,
