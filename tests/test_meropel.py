@@ -92,18 +92,17 @@ def test_updates_with_terms_and_norms_of_their_own_pass_to_the_next_norm():
     u = Normed(Combined(["a", "b"]), torch.ones(4), 1e-5)
     assert split_update(u) == (u, None)
     norm = PartSpec("rmsnorm", dict(width=8, eps=1e-5, weight="w"))
-    blk = build_part("block", PartSpec("prenorm", dict(
-        mixer=PartSpec("gated_linear_attention", dict(width=8, n_heads=1, head_dim=4, v_head_dim=4, tau=2.0, names={
-            k: k for k in ("q", "k", "v", "g", "o", "norm", "a1", "a2", "a2_bias")})),
-        feed_forward=None, norm_mixer=norm, norm_feed_forward=None, post_norm_mixer=PartSpec("rmsnorm", dict(width=8, eps=1e-5, weight="wb")),
-        post_norm_feed_forward=PartSpec("rmsnorm", dict(width=8, eps=1e-5, weight="wc")))))
+    mixer = PartSpec("gated_linear_attention", dict(width=8, n_heads=1, head_dim=4, v_head_dim=4, tau=2.0, names={
+        k: k for k in ("q", "k", "v", "g", "o", "norm", "a1", "a2", "a2_bias")}))
+
+    def block(post_mixer, post_ffn):
+        return build_part("block", PartSpec("prenorm", dict(mixer=mixer, feed_forward=None, norm_mixer=norm, norm_feed_forward=None,
+                                                            post_norm_mixer=post_mixer, post_norm_feed_forward=post_ffn)))
+    blk = block(PartSpec("rmsnorm", dict(width=8, eps=1e-5, weight="wb")), PartSpec("rmsnorm", dict(width=8, eps=1e-5, weight="wc")))
     assert blk.post_mixer is not None and blk.post_ffn is None      # no feed-forward: its output norm is not built
     assert "wb" in [p.name for p in blk.params()] and "wc" not in [p.name for p in blk.params()]
-    with pytest.raises(TypeError):
-        build_part("block", PartSpec("prenorm", dict(mixer=blk._mixer and PartSpec("gated_linear_attention", dict(
-            width=8, n_heads=1, head_dim=4, v_head_dim=4, tau=2.0, names={k: k for k in ("q", "k", "v", "g", "o", "norm", "a1", "a2", "a2_bias")})),
-            feed_forward=None, norm_mixer=norm, norm_feed_forward=None,
-            post_norm_mixer=PartSpec("rmsnorm", dict(width=8, eps=1e-5, weight="wb", groups=2)))))
+    with pytest.raises(TypeError):      # a norm on a sublayer's output is a plain RMSNorm, not one in groups
+        block(PartSpec("rmsnorm", dict(width=8, eps=1e-5, weight="wb", groups=2)), None)
 
 
 def test_side_by_side_takes_one_cache_and_one_state():
